@@ -47,6 +47,11 @@ class KVView:
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
+    v_head_dim: int = 0        # width of a value row per head (0: the same as head_dim)
+
+    def __post_init__(self):
+        if not self.v_head_dim:
+            self.v_head_dim = self.head_dim
 
 
 class KVGroup:
@@ -149,9 +154,10 @@ class KVGroup:
 
     def view(self, cache_id: int) -> KVView:
         i = self.index[cache_id]
+        kr, vr = self.need.key_row(), self.need.value_row()
         return KVView(k=self.k[i], v=self.v[i], table=self.table, ring=self.ring,
-                      n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
-                      window=self.need.window)
+                      n_kv_heads=self.need.n_kv_heads or kr[0], head_dim=self.need.head_dim or kr[-1],
+                      window=self.need.window, v_head_dim=vr[-1])
 
     def bytes(self) -> int:
         return self.k.numel() * self.k.element_size() + self.v.numel() * self.v.element_size()

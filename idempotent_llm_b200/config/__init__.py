@@ -1,8 +1,12 @@
 """Typed configurations and the architecture-neutral specs they translate to."""
 
-from .specs import (AttentionSpec, ConfigError, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
-                    RotarySpec, RunEntry, default_schedule)
+from .specs import (AttentionSpec, ConfigError, GatedMLPSpec, LayerSpec, MixerBranch, ModelSpec, NormSpec,
+                    ParallelMixerSpec, RotarySpec, RunEntry, SandwichLayerSpec, SinkAttentionSpec, SSDSpec,
+                    TokenSideSpec, WavelengthScaling, default_schedule)
 from .qwen3 import Qwen3Config
+from .lunulix import LunulixConfig
 
 __all__ = ["AttentionSpec", "ConfigError", "GatedMLPSpec", "LayerSpec", "ModelSpec", "NormSpec",
-           "RotarySpec", "RunEntry", "default_schedule", "Qwen3Config"]
+           "RotarySpec", "RunEntry", "default_schedule", "Qwen3Config", "LunulixConfig", "MixerBranch",
+           "ParallelMixerSpec", "SandwichLayerSpec", "SinkAttentionSpec", "SSDSpec", "TokenSideSpec",
+           "WavelengthScaling"]

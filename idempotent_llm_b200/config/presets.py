@@ -23,7 +23,7 @@ def preset_dict(name: str) -> dict:
 
 def preset(name: str, **overrides):
     """The typed configuration of a preset, through the registry like any config.json."""
-    from ..registry import architecture
+    from ..registry import architecture, architecture_name
     d = preset_dict(name)
     d.update(overrides)
-    return architecture(d["architectures"][0]).config_class.from_dict(d)
+    return architecture(architecture_name(d, name)).config_class.from_dict(d)

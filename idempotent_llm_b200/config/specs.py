@@ -38,6 +38,20 @@ class RotarySpec:
     max_positions: int
     variant: str = "half_whole_head"
     kind: str = "rotary"
+    scaling: Optional["WavelengthScaling"] = None
+
+
+@dataclass(frozen=True)
+class WavelengthScaling:
+    """Frequencies rescaled by wavelength ``l = 2 pi / f`` against a trained length ``original``: waves shorter
+    than ``original / high`` are kept, waves longer than ``original / low`` are divided by ``factor``, and
+    between the two the frequency is ``(1 - s) f / factor + s f`` with ``s = (original / l - low) /
+    (high - low)``."""
+
+    factor: float
+    low: float
+    high: float
+    original: float
 
 
 @dataclass(frozen=True)
@@ -112,6 +126,136 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class SinkAttentionNames:
+    """Checkpoint names of a gated attention with short filters and a sink, behind the mixer's prefix; a filter's
+    tensor is its projection's name plus ``conv``."""
+
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    gate: str = "g"
+    sink: str = "sink"
+    conv: str = ".conv"
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Causal grouped-query attention (a *mixer*) with, each optional: a short causal filter over time on
+    every channel of q, k and v (``conv_taps`` > 1) directly behind the projections; a rotation of the first
+    ``position.dim`` dims of each q and k head (variant ``"half_partial"``: dim i with dim i + dim / 2, the rest
+    untouched); one learned score per head that joins the softmax's denominator with no key and no value
+    (``sink``); the merged heads times ``sigmoid(gate projection of the mixer's input)`` before the output
+    projection (``gate``).  Keys have ``key_dim`` and values ``value_dim`` elements per head."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    softmax_scale: float
+    conv_taps: int = 1
+    position: Optional[RotarySpec] = None
+    sink: bool = True
+    gate: bool = True
+    names: SinkAttentionNames = SinkAttentionNames()
+    kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
+class SSDNames:
+    """Checkpoint names of a state-space mixer, behind the mixer's prefix."""
+
+    w_in: str = "in"
+    conv: str = "conv"
+    conv_bias: str = "conv.b"
+    dt_bias: str = "dt_bias"
+    a_log: str = "A_log"
+    d: str = "D"
+    norm: str = "norm"
+    o: str = "o"
+
+
+@dataclass(frozen=True)
+class SSDSpec:
+    """Selective state-space mixer with a scalar decay per head (the state-space duality form).  The input
+    projection's rows are ``[z: inner | x: inner | B: groups * state | C: groups * state | dt: heads]`` with
+    ``inner = heads * head_dim``; x, B and C pass a causal filter of ``conv_taps`` taps with bias and silu;
+    ``dt = softplus(dt + dt_bias)``; per head ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D x``;
+    ``y * silu(z)`` is normed in ``norm_groups`` equal parts (each by its own root mean square), times a
+    weight; then the output projection."""
+
+    hidden: int
+    heads: int
+    head_dim: int
+    state: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    names: SSDNames = SSDNames()
+    kind: str = "ssd"
+
+
+@dataclass(frozen=True)
+class MixerBranch:
+    """One of the mixers of a ``ParallelMixerSpec``: its spec, the prefix of its tensors behind the parallel
+    mixer's own, and the constant its output is multiplied with."""
+
+    mixer: object
+    prefix: str
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side that read the same input; the result is the sum of their outputs, each times
+    its constant.  At most one branch keeps keys and values; any may keep per-sequence state."""
+
+    hidden: int
+    branches: Tuple[MixerBranch, ...]
+    prefix: str = ""
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input that depends on the token itself: ``g = act(gate h) * e`` with ``e`` the columns
+    ``[col0, col0 + dim)`` of the token's row of a second embedding table shared by all layers; ``y = proj g``;
+    ``h += y / sqrt(mean(y^2) + eps) * norm``."""
+
+    hidden: int
+    dim: int
+    col0: int
+    vocab_size: int
+    table_width: int
+    eps: float
+    table: str                      # the shared table's checkpoint name (no layer prefix)
+    gate: str = "side.gate"
+    proj: str = "side.proj"
+    norm: str = "side.norm"
+    activation: str = "gelu_tanh"
+    kind: str = "token_side"
+
+
+@dataclass(frozen=True)
+class SandwichLayerSpec:
+    """A layer that norms every sublayer's input AND output: ``h += post(mixer(pre(h)))``, then, if it has a
+    feed-forward, ``h += post(ff(pre(h)))``, then, if it has one, the token side input.  The four norms'
+    tensors are ``prefix + <NormSpec.weight>``."""
+
+    prefix: str
+    mixer: object
+    mixer_norm: NormSpec
+    mixer_post_norm: NormSpec
+    feed_forward: Optional[object] = None
+    feed_forward_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    token_side: Optional[TokenSideSpec] = None
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: which block arrangement, and the parts inside it.
 
@@ -160,6 +304,7 @@ class ModelSpec:
     head_name: str
     stop_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02
+    embed_scale: float = 1.0            # the embedding row is multiplied with this constant
     extra: dict = field(default_factory=dict, compare=False)
 
     def __post_init__(self):

@@ -22,6 +22,12 @@ struct AttnArgs {
     const int* token_seq; const int* positions; const int* slots; const int* q_start; const int* cu_q;
     int n_tokens, n_q, n_kv, hd;
     float scale; int window;
+    // beyond plain attention (all off in idm_attention_generic):
+    int dv;                       // width of a value row (keys have hd)
+    const float* sink;            // [n_q] or null: exp(sink[head]) joins the softmax's denominator, with no key and no value
+    const float* gate; int gate_stride;   // or null: out *= sigmoid(gate[t * gate_stride + head * dv + d])
+    int out_stride, out_col;      // out[t * out_stride + out_col + head * dv + d]
+    float out_scale;
 };
 
 #define AG_WARPS 4
@@ -42,7 +48,8 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
     const int pos = a.positions[t], s = a.token_seq[t], slot = a.slots[s];
     const int first_new = a.k_new ? a.q_start[s] : 0x7fffffff, tok0 = a.cu_q[s];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    float m = -INFINITY, l = 0.f;
+    // a sink is a key of score sink[head] (not scaled) whose value is zero: the sums start from it
+    float m = a.sink ? a.sink[head] : -INFINITY, l = a.sink ? 1.f : 0.f;
     float acc[IDM_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
@@ -54,11 +61,11 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
         if (valid) {
             const T* krow;
             if (j >= first_new) {
-                const size_t off = ((size_t)(tok0 + j - first_new) * a.n_kv + g) * a.hd;
-                krow = a.k_new + off; vrow = a.v_new + off;
+                const size_t row = (size_t)(tok0 + j - first_new) * a.n_kv + g;
+                krow = a.k_new + row * a.hd; vrow = a.v_new + row * a.dv;
             } else {
-                const size_t off = kv_offset(a.cache, slot, j, g);
-                krow = a.cache.k + off; vrow = a.cache.v + off;
+                const size_t row = kv_row(a.cache, slot, j, g);
+                krow = a.cache.k + row * a.hd; vrow = a.cache.v + row * a.dv;
             }
             float dot = 0.f;
             for (int d = 0; d < a.hd; d += Vec16<T>::N) {
@@ -83,17 +90,31 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
 #pragma unroll
             for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < a.hd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+                if (d < a.dv) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
             }
         }
     }
-    T* orow = a.out + ((size_t)t * a.n_q + head) * a.hd;
+    T* orow = a.out + (size_t)t * a.out_stride + a.out_col + (size_t)head * a.dv;
     const float inv = 1.0f / l;
+    const float* grow = a.gate ? a.gate + (size_t)t * a.gate_stride + (size_t)head * a.dv : nullptr;
 #pragma unroll
     for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < a.hd) from_f32(orow[d], acc[i] * inv);
+        if (d < a.dv) {
+            float o = acc[i] * inv;
+            if (grow) o = o / (1.0f + expf(-grow[d]));
+            if (a.out_scale != 1.f) o *= a.out_scale;
+            from_f32(orow[d], o);
+        }
     }
+}
+
+static int attention_generic_launch(AttnArgs& a, cudaStream_t stream) {
+    const long long warps = (long long)a.n_tokens * a.n_q;
+    idm_launch(attention_generic_kernel, dim3((unsigned)((warps + AG_WARPS - 1) / AG_WARPS)), dim3(AG_WARPS * 32),
+               AG_WARPS * a.hd * sizeof(float), stream, a);
+    IDM_LAUNCH_CHECK("attention_generic");
+    return 0;
 }
 
 extern "C" int idm_attention_generic(const void* q, void* out, void* k_pool, void* v_pool, const int* table,
@@ -113,8 +134,34 @@ extern "C" int idm_attention_generic(const void* q, void* out, void* k_pool, voi
     a.k_new = (const T*)k_new; a.v_new = (const T*)v_new;
     a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
-    const long long warps = (long long)n_tokens * n_q;
-    idm_launch(attention_generic_kernel, dim3((unsigned)((warps + AG_WARPS - 1) / AG_WARPS)), dim3(AG_WARPS * 32), AG_WARPS * hd * sizeof(float), stream, a);
-    IDM_LAUNCH_CHECK("attention_generic");
-    return 0;
+    a.dv = hd; a.sink = nullptr; a.gate = nullptr; a.gate_stride = 0; a.out_stride = n_q * hd; a.out_col = 0; a.out_scale = 1.f;
+    return attention_generic_launch(a, stream);
+}
+
+// The same walk over the cache with what a gated attention with a sink adds: value rows of their own width
+// `dv`, a learned score per head that joins the softmax's denominator without a key or a value, and the
+// result times sigmoid(gate) times a constant, stored at a column offset of a wider buffer (gate: 32-bit
+// [N, gate_stride], columns head * dv + d).  All keys come from the cache.
+extern "C" int idm_attention_sink(const void* q, void* out, int out_stride, int out_col, float out_scale,
+                                  void* k_pool, void* v_pool, const int* table, int table_stride,
+                                  const float* sink, const float* gate, int gate_stride,
+                                  const int* token_seq, const int* positions, const int* slots,
+                                  const int* q_start, const int* cu_q, int n_tokens, int n_q, int n_kv,
+                                  int hd, int dv, float scale, int window, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(hd > 0 && hd % Vec16<T>::N == 0 && hd <= IDM_MAX_HEAD_DIM && dv > 0 && dv <= IDM_MAX_HEAD_DIM,
+                "attention: key size %d must be a multiple of %d, key and value sizes (%d) at most %d", hd, Vec16<T>::N, dv,
+                IDM_MAX_HEAD_DIM);
+    IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d q-heads are no multiple of %d kv-heads", n_q, n_kv);
+    IDM_REQUIRE(out_col >= 0 && out_col + n_q * dv <= out_stride, "attention: columns %d..%d of rows of %d", out_col,
+                out_col + n_q * dv, out_stride);
+    AttnArgs a;
+    a.q = (const T*)q; a.out = (T*)out;
+    a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, 0, n_kv, hd};
+    a.k_new = nullptr; a.v_new = nullptr;
+    a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
+    a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
+    a.dv = dv; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride; a.out_stride = out_stride; a.out_col = out_col;
+    a.out_scale = out_scale;
+    return attention_generic_launch(a, stream);
 }

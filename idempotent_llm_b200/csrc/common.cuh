@@ -142,6 +142,17 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 #endif
 }
 
+// Gated activations by number.  act 0: g * sigmoid(g) * u (silu_mul);  act 1: the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u.  One formula each, wherever it is applied: the epilogue
+// of a gate/up product and the kernel of its own give the same bits.
+__device__ __forceinline__ float gelu_tanh_f(float g) {
+    const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+    return 0.5f * g * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float gated_act(float g, float u, int act) {
+    return act == 1 ? gelu_tanh_f(g) * u : silu_mul(g, u);
+}
+
 // ------------------------------------------------------------ reductions
 // Fixed-order reductions: xor butterflies inside a warp, then the warps' values
 // added in ascending order.  The order depends on the block size only.
@@ -209,8 +220,12 @@ struct KVAddr {
     int n_kv;
     int hd;
 };
-__device__ __forceinline__ size_t kv_offset(const KVAddr& c, int slot, int j, int kv_head) {
+// the row of key j of a kv-head among all rows of the pool (key rows and value rows may differ in width)
+__device__ __forceinline__ size_t kv_row(const KVAddr& c, int slot, int j, int kv_head) {
     const int r = c.ring ? (j % c.ring) : j;
     const int page = c.table[(size_t)slot * c.table_stride + (r / IDM_PAGE)];
-    return (((size_t)page * c.n_kv + kv_head) * IDM_PAGE + (r % IDM_PAGE)) * (size_t)c.hd;
+    return ((size_t)page * c.n_kv + kv_head) * IDM_PAGE + (r % IDM_PAGE);
+}
+__device__ __forceinline__ size_t kv_offset(const KVAddr& c, int slot, int j, int kv_head) {
+    return kv_row(c, slot, j, kv_head) * (size_t)c.hd;
 }

@@ -327,3 +327,120 @@ extern "C" int idm_swiglu(const float* gu, int n_partials, long long partial_str
     }
     return 0;
 }
+
+// ------------------------------------------------------------ scaled embedding
+// h[t, :] = table[tokens[t], :] * scale, the product rounded once in 32-bit
+__global__ void embed_scaled_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                    float* __restrict__ h, int hidden, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)tokens[t] * hidden;
+    float* out = h + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
+}
+
+extern "C" int idm_embed_scaled(const int* tokens, const void* table, float* h, int n_tokens, int hidden,
+                                float scale, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(n_tokens > 0 && hidden > 0, "embed: bad sizes n_tokens=%d hidden=%d", n_tokens, hidden);
+    idm_launch(embed_scaled_kernel, dim3(n_tokens), dim3(256), 0, stream, tokens, (const T*)table, h, hidden, scale);
+    IDM_LAUNCH_CHECK("embed_scaled");
+    return 0;
+}
+
+// ------------------------------------------- norm behind a sublayer, and the next one before
+// For layers that norm a sublayer's output before adding it:
+//   h[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w_post          (32-bit, stored)
+// and, in the same pass over the row, what the next sublayer reads:
+//   mode 1: x[r] = h[r] / sqrt(mean(h[r]^2) + eps_pre) * w_pre;   mode 2: x[r] = h[r];   mode 0: nothing.
+// One block per row, the row kept in shared memory between the passes.
+__global__ void __launch_bounds__(256) post_pre_norm_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                                            const float* __restrict__ w_post, float eps,
+                                                            const float* __restrict__ w_pre, float eps_pre,
+                                                            T* __restrict__ x, int mode, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    extern __shared__ float vals[];
+    const size_t r = blockIdx.x;
+    const float* yr = y + r * hidden;
+    float* hr = h + r * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) { const float v = yr[c]; vals[c] = v; ss = fmaf(v, v, ss); }
+    float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = hr[c] + vals[c] * inv * w_post[c];
+        hr[c] = v; vals[c] = v; ss = fmaf(v, v, ss);
+    }
+    if (mode == 0) return;
+    T* xr = x + r * hidden;
+    if (mode == 2) {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) from_f32(xr[c], vals[c]);
+        return;
+    }
+    inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps_pre);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) from_f32(xr[c], vals[c] * inv * w_pre[c]);
+}
+
+extern "C" int idm_post_pre_norm(float* h, const float* y, const float* w_post, float eps, const float* w_pre,
+                                 float eps_pre, void* x, int mode, int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    IDM_REQUIRE(hidden > 0 && n_rows > 0 && mode >= 0 && mode <= 2, "post_pre_norm: rows=%d hidden=%d mode=%d", n_rows, hidden, mode);
+    IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "post_pre_norm: hidden=%d does not fit shared memory", hidden);
+    IDM_REQUIRE(mode == 0 || x != nullptr, "post_pre_norm: mode %d needs an output", mode);
+    IDM_REQUIRE(mode != 1 || w_pre != nullptr, "post_pre_norm: mode 1 needs the next norm's weight");
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(post_pre_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    idm_launch(post_pre_norm_kernel, dim3(n_rows), dim3(256), smem, stream, h, y, w_post, eps, w_pre, eps_pre, (T*)x, mode, hidden);
+    IDM_LAUNCH_CHECK("post_pre_norm");
+    return 0;
+}
+
+// ------------------------------------------------------ gated activations, by name
+// (gated_act in common.cuh: act 0 is g * sigmoid(g) * u, act 1 the tanh form of gelu times u)
+
+// y[t, i] = act(gu[t, i]) * gu[t, inter + i] of a 32-bit gate/up product [N, 2 * inter]
+__global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict__ gu, T* __restrict__ y, int inter, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= inter) return;
+    const size_t t = blockIdx.x;
+    from_f32(y[t * (size_t)inter + c], gated_act(gu[t * 2 * (size_t)inter + c], gu[t * 2 * (size_t)inter + inter + c], act));
+}
+
+extern "C" int idm_gated_act(const float* gu, void* y, int n_tokens, int inter, int act, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(inter > 0 && (act == 0 || act == 1), "gated_act: inter=%d act=%d", inter, act);
+    idm_launch(gated_act_kernel, dim3(n_tokens, (inter + 255) / 256), dim3(256), 0, stream, gu, (T*)y, inter, act);
+    IDM_LAUNCH_CHECK("gated_act");
+    return 0;
+}
+
+// y[t, j] = act(s[t, j]) * table[tokens[t], col0 + j]: a projection gated by a slice of the token's own row
+// of a second embedding table [vocab, table_width]
+__global__ void __launch_bounds__(256) token_gate_kernel(const float* __restrict__ s, const int* __restrict__ tokens,
+                                                         const T* __restrict__ table, int table_width, int col0,
+                                                         T* __restrict__ y, int dim, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= dim) return;
+    const size_t t = blockIdx.x;
+    const float e = to_f32(table[(size_t)tokens[t] * table_width + col0 + j]);
+    from_f32(y[t * (size_t)dim + j], gated_act(s[t * (size_t)dim + j], e, act));
+}
+
+extern "C" int idm_token_gate(const float* s, const int* tokens, const void* table, int table_width, int col0,
+                              void* y, int n_tokens, int dim, int act, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(dim > 0 && col0 >= 0 && col0 + dim <= table_width && (act == 0 || act == 1),
+                "token_gate: columns %d..%d of rows of %d, act=%d", col0, col0 + dim, table_width, act);
+    idm_launch(token_gate_kernel, dim3(n_tokens, (dim + 255) / 256), dim3(256), 0, stream, s, tokens, (const T*)table,
+               table_width, col0, (T*)y, dim, act);
+    IDM_LAUNCH_CHECK("token_gate");
+    return 0;
+}

@@ -98,6 +98,7 @@ enum { EPI_STORE = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 struct GemmEpi {
     float* out;          // STORE: [M, N]; RESIDUAL: the residual stream [M, N]
     T* y; int inter;     // SWIGLU: y [M, inter]
+    int act;             // SWIGLU: which gated activation (gated_act in common.cuh; 0 = silu)
     QkvArgs q;           // QKV
 };
 
@@ -192,8 +193,8 @@ __device__ __forceinline__ void persistent_tile_epilogue(const GemmEpi& e, uint3
                 if (j < cols) {
                     const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + sub * 16);
                     const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
-                    const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
-                                         silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
+                    const float y8[8] = {gated_act(p0.x, p0.y, e.act), gated_act(p0.z, p0.w, e.act), gated_act(p1.x, p1.y, e.act), gated_act(p1.z, p1.w, e.act),
+                                         gated_act(p2.x, p2.y, e.act), gated_act(p2.z, p2.w, e.act), gated_act(p3.x, p3.y, e.act), gated_act(p3.z, p3.w, e.act)};
                     const int fg = tx * 64 + sub * 8;
                     T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
                     if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
@@ -1052,7 +1053,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                             float y8[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
-                                y8[i] = silu_mul(__uint_as_float(raw[16 * h + 2 * i]), __uint_as_float(raw[16 * h + 2 * i + 1]));
+                                y8[i] = gated_act(__uint_as_float(raw[16 * h + 2 * i]), __uint_as_float(raw[16 * h + 2 * i + 1]), e.act);
                             T* dst = e.y + (size_t)t * e.inter + fg;
                             if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
                                 store8(dst, y8);
@@ -1438,6 +1439,16 @@ extern "C" int idm_gemm_bf16_swiglu(const void* x, const void* w_tiled, void* y,
                                     cudaStream_t stream) {
     GemmEpi e = {};
     e.y = (T*)y; e.inter = inter;
+    const int tiles = (inter + 63) / 64;
+    return gemm_any<EPI_SWIGLU>(x, w_tiled, e, M, tiles * GT_BM, K, stream);
+}
+
+// the same product with the gated activation chosen by number (gated_act in common.cuh): y = act(x . gate^T) * (x . up^T)
+extern "C" int idm_gemm_bf16_gated(const void* x, const void* w_tiled, void* y, int M, int inter, int K, int act,
+                                   cudaStream_t stream) {
+    IDM_REQUIRE(act == 0 || act == 1, "gemm_gated: activation %d is not built", act);
+    GemmEpi e = {};
+    e.y = (T*)y; e.inter = inter; e.act = act;
     const int tiles = (inter + 63) / 64;
     return gemm_any<EPI_SWIGLU>(x, w_tiled, e, M, tiles * GT_BM, K, stream);
 }

@@ -1,0 +1,168 @@
+// The recurrence of a selective state-space mixer (state-space duality form, scalar decay per head),
+// token by token in 32-bit, with the state of every sequence carried from step to step:
+//
+//   dt_t = softplus(raw_t + dt_bias_h)            a_h = exp(A_log_h)
+//   S_t  = exp(-a_h dt_t) S_(t-1) + dt_t B_t x_t^T     (S: [N, P] per head)
+//   y_t  = S_t^T C_t + D_h x_t,   then  y_t * silu(z_t)
+//
+// x [N_tok, heads, P], B and C [N_tok, groups, N] are columns of one 32-bit buffer (the filtered
+// projection), z and the raw step sizes columns of another (the projection itself).  Head h reads group
+// h / (heads / groups).  One block owns (sequence, head, a slice of P) and walks the sequence's tokens of
+// this step in order; a thread keeps N / 4 state elements of one column p in registers, four threads
+// share a column and add their parts of y by shuffles in a fixed order.  A step of one token and a step
+// of a thousand run the same operations on the same numbers for every token.
+//
+// ssd_group_norm: the gated output in `parts` equal parts, each divided by its own root mean square,
+// times a weight and a constant, stored in the storage type at a column offset of a wider buffer.
+#include "common.cuh"
+
+#define SSD_NS 4            // threads per column of the state
+#define SSD_PB 32           // columns of the state per block
+#define SSD_CHUNK 8         // tokens staged in shared memory at a time
+
+struct SsdArgs {
+    const float* xbc; int xbc_stride; int x_col, b_col, c_col;    // filtered projection
+    const float* proj; int proj_stride; int z_col, dt_col;        // projection: gate and raw step sizes
+    const float* dt_bias; const float* a_log; const float* d_skip;
+    float* state; long long state_stride;                          // state + slot * stride : [heads, N, P]
+    float* y; int y_stride;                                        // [N_tok, heads * P] gated output
+    const int* cu_q; const int* slots;
+    int heads, groups, P, N;
+};
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+template <int NPT>
+__global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int s = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SSD_PB;
+    const int g = h / (a.heads / a.groups);
+    const int pl = threadIdx.x / SSD_NS, ns = threadIdx.x % SSD_NS;
+    const int p = p0 + pl;
+    const bool live = p < a.P;
+    const int t0 = a.cu_q[s], t1 = a.cu_q[s + 1];
+    float* sB = sm;                              // [CHUNK][N]
+    float* sC = sB + SSD_CHUNK * a.N;            // [CHUNK][N]
+    float* sX = sC + SSD_CHUNK * a.N;            // [CHUNK][PB]
+    float* sZ = sX + SSD_CHUNK * SSD_PB;         // [CHUNK][PB]
+    float* sDt = sZ + SSD_CHUNK * SSD_PB;        // [CHUNK] step sizes, [CHUNK] decays
+    float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * a.N * a.P;
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = ns * NPT + i;
+        S[i] = (live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
+    }
+    const float neg_a = -expf(a.a_log[h]), dskip = a.d_skip[h], bias = a.dt_bias[h];
+    for (int tc = t0; tc < t1; tc += SSD_CHUNK) {
+        const int nt = min(SSD_CHUNK, t1 - tc);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * a.N; i += blockDim.x) {
+            const int tt = i / a.N, n = i % a.N;
+            const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride;
+            sB[tt * a.N + n] = row[a.b_col + g * a.N + n];
+            sC[tt * a.N + n] = row[a.c_col + g * a.N + n];
+        }
+        for (int i = threadIdx.x; i < nt * SSD_PB; i += blockDim.x) {
+            const int tt = i / SSD_PB, pp = p0 + i % SSD_PB;
+            const bool in = pp < a.P;
+            sX[i] = in ? a.xbc[(size_t)(tc + tt) * a.xbc_stride + a.x_col + h * a.P + pp] : 0.f;
+            sZ[i] = in ? a.proj[(size_t)(tc + tt) * a.proj_stride + a.z_col + h * a.P + pp] : 0.f;
+        }
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f(a.proj[(size_t)(tc + threadIdx.x) * a.proj_stride + a.dt_col + h] + bias);
+            sDt[threadIdx.x] = dt;
+            sDt[SSD_CHUNK + threadIdx.x] = expf(neg_a * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float dt = sDt[tt], decay = sDt[SSD_CHUNK + tt];
+            const float x = sX[tt * SSD_PB + pl];
+            const float dtx = dt * x;
+            const float* Bt = sB + tt * a.N + ns * NPT;
+            const float* Ct = sC + tt * a.N + ns * NPT;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                if (ns * NPT + i < a.N) {
+                    S[i] = fmaf(decay, S[i], dtx * Bt[i]);
+                    acc = fmaf(S[i], Ct[i], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (ns == 0 && live) {
+                const float z = sZ[tt * SSD_PB + pl];
+                const float yv = fmaf(dskip, x, acc);
+                a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = ns * NPT + i;
+        if (live && n < a.N) st[(size_t)n * a.P + p] = S[i];
+    }
+}
+
+extern "C" int idm_ssd_scan(const float* xbc, int xbc_stride, int x_col, int b_col, int c_col, const float* proj,
+                            int proj_stride, int z_col, int dt_col, const float* dt_bias, const float* a_log,
+                            const float* d_skip, float* state, long long state_stride, float* y, int y_stride,
+                            const int* cu_q, const int* slots, int n_seqs, int heads, int groups, int P, int N,
+                            cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    IDM_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && P > 0 && N > 0 && N <= 256,
+                "ssd_scan: %d heads in %d groups, columns %d, state %d (at most 256)", heads, groups, P, N);
+    IDM_REQUIRE(state_stride >= (long long)heads * N * P, "ssd_scan: a slot's state must hold %d x %d x %d floats", heads, N, P);
+    IDM_REQUIRE(n_seqs <= 65535 && heads <= 65535, "ssd_scan: %d sequences, %d heads in one launch", n_seqs, heads);
+    SsdArgs a;
+    a.xbc = xbc; a.xbc_stride = xbc_stride; a.x_col = x_col; a.b_col = b_col; a.c_col = c_col;
+    a.proj = proj; a.proj_stride = proj_stride; a.z_col = z_col; a.dt_col = dt_col;
+    a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.state = state; a.state_stride = state_stride;
+    a.y = y; a.y_stride = y_stride; a.cu_q = cu_q; a.slots = slots;
+    a.heads = heads; a.groups = groups; a.P = P; a.N = N;
+    const dim3 grid(n_seqs, heads, (P + SSD_PB - 1) / SSD_PB), block(SSD_NS * SSD_PB);
+    const size_t smem = (size_t)(2 * SSD_CHUNK * N + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
+    const int npt = (N + SSD_NS - 1) / SSD_NS;
+    if (npt <= 8) idm_launch(ssd_scan_kernel<8>, grid, block, smem, stream, a);
+    else if (npt <= 16) idm_launch(ssd_scan_kernel<16>, grid, block, smem, stream, a);
+    else if (npt <= 32) idm_launch(ssd_scan_kernel<32>, grid, block, smem, stream, a);
+    else idm_launch(ssd_scan_kernel<64>, grid, block, smem, stream, a);
+    IDM_LAUNCH_CHECK("ssd_scan");
+    return 0;
+}
+
+// out[t, out_col + c] = y[t, c] / sqrt(mean over c's part of y^2 + eps) * w[c] * scale.  One warp per (token, part).
+__global__ void __launch_bounds__(128) ssd_group_norm_kernel(const float* __restrict__ y, int width, int parts,
+                                                             const float* __restrict__ w, float eps, float scale,
+                                                             T* __restrict__ out, int out_stride, int out_col, int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)n_tokens * parts) return;
+    const int t = (int)(wid / parts), part = (int)(wid % parts), len = width / parts;
+    const float* row = y + (size_t)t * width + (size_t)part * len;
+    float ss = 0.f;
+    for (int c = lane; c < len; c += 32) ss = fmaf(row[c], row[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)len + eps);
+    T* o = out + (size_t)t * out_stride + out_col + (size_t)part * len;
+    const float* wp = w + (size_t)part * len;
+    for (int c = lane; c < len; c += 32) from_f32(o[c], row[c] * inv * wp[c] * scale);
+}
+
+extern "C" int idm_ssd_group_norm(const float* y, int width, int parts, const float* w, float eps, float scale,
+                                  void* out, int out_stride, int out_col, int n_tokens, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(width > 0 && parts > 0 && width % parts == 0, "ssd_group_norm: %d columns in %d parts", width, parts);
+    IDM_REQUIRE(out_col >= 0 && out_col + width <= out_stride, "ssd_group_norm: columns %d..%d of rows of %d", out_col,
+                out_col + width, out_stride);
+    const long long warps = (long long)n_tokens * parts;
+    idm_launch(ssd_group_norm_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, y, width, parts, w, eps, scale,
+               (T*)out, out_stride, out_col, n_tokens);
+    IDM_LAUNCH_CHECK("ssd_group_norm");
+    return 0;
+}

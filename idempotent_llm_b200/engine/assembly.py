@@ -24,12 +24,16 @@ def declare_weights(spec: ModelSpec) -> List[TensorDecl]:
     decls += NORMS.get(spec.final_norm.kind).declare(spec.final_norm, spec.final_norm_prefix)
     # tied: an lm_head in the file is tolerated and ignored; untied: it is required
     decls.append(TensorDecl(spec.head_name, (spec.vocab_size, spec.hidden), optional=spec.tie_embeddings))
-    seen = set()
+    # a tensor that several parts share (a table all layers read) is declared by each of them, alike
+    seen, unique = {}, []
     for d in decls:
         if d.name in seen:
-            raise ValueError(f"tensor {d.name} is declared twice")
-        seen.add(d.name)
-    return decls
+            if seen[d.name] != d:
+                raise ValueError(f"tensor {d.name} is declared twice, differently")
+            continue
+        seen[d.name] = d
+        unique.append(d)
+    return unique
 
 
 def cache_needs(spec: ModelSpec) -> Dict[int, CacheNeed]:
@@ -76,6 +80,8 @@ class CausalLM:
         from ..kernels.program import NotProgrammable, StepProgram
         hidden = self.spec.hidden
         try:
+            if float(getattr(self.spec, "embed_scale", 1.0)) != 1.0:
+                raise NotProgrammable("a scaled embedding is called from forward")
             prog = StepProgram(K)
             h = prog.buffer("stream", per_token=4 * hidden)
             prog.embed(self.embed, h)
@@ -102,7 +108,8 @@ class CausalLM:
             prog = self.program(cache)
             if prog is not None:
                 return prog.run(ctx, want_rows)
-        h = K.embed(ctx.tokens, self.embed)
+        scale = float(getattr(self.spec, "embed_scale", 1.0))
+        h = K.embed(ctx.tokens, self.embed) if scale == 1.0 else K.embed_scaled(ctx.tokens, self.embed, scale)
         pending = None
         for e in self.spec.schedule:
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, cache.view(e.cache),

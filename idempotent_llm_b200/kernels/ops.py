@@ -58,6 +58,17 @@ SIGNATURES = {
     "idm_page_tokens": (c_int, ""),
     "idm_set_pdl": (None, "i"),
     "idm_embed": (c_int, "pppiip"),
+    "idm_embed_scaled": (c_int, "pppiifp"),
+    "idm_post_pre_norm": (c_int, "pppfpfpiiip"),
+    "idm_gated_act": (c_int, "ppiiip"),
+    "idm_token_gate": (c_int, "pppiipiiip"),
+    "idm_short_conv": (c_int, "piiiippipqppppppip"),
+    "idm_conv_qkv_cache": (c_int, "piiippqiiiiipppppipppppip"),
+    "idm_conv_state_update": (c_int, "piiiipqppppip"),
+    "idm_ssd_scan": (c_int, "piiiipiiippppqpippiiiiip"),
+    "idm_ssd_group_norm": (c_int, "piipffpiiip"),
+    "idm_attention_sink": (c_int, "ppiifpppippipppppiiiiifip"),
+    "idm_gemm_bf16_gated": (c_int, "pppiiiip"),
     "idm_add_rmsnorm": (c_int, "ppiqpfppiip"),
     "idm_rope_table": (c_int, "ppppiip"),
     "idm_qkv_finish": (c_int, "piqiiiippfpppppppiipppp"),
@@ -198,6 +209,142 @@ class Kernels:
                                        n, hidden, self._stream()))
         return h
 
+    def embed_scaled(self, tokens: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+        """``table[tokens] * scale`` as the 32-bit stream."""
+        self._need(tokens, torch.int32, "embed tokens")
+        self._need(table, self.dtype, "embed table")
+        n, hidden = tokens.numel(), table.shape[1]
+        h = torch.empty((n, hidden), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_embed_scaled(_p(tokens), _p(table), _p(h), n, hidden, float(scale), self._stream()))
+        return h
+
+    def post_pre_norm(self, h, y, w_post, eps: float, w_pre=None, eps_pre: float = 0.0, cast: bool = False):
+        """``h += rmsnorm(y) * w_post`` in place; returns what the next sublayer reads: ``rmsnorm(h) * w_pre`` if
+        ``w_pre`` is given, ``h`` in the storage dtype if ``cast``, else None."""
+        self._need(h, torch.float32, "residual stream")
+        self._need(y, torch.float32, "sublayer output")
+        n, hidden = h.shape
+        if tuple(y.shape) != (n, hidden) or w_post.numel() != hidden or (w_pre is not None and w_pre.numel() != hidden):
+            raise KernelError(f"post_pre_norm: stream {tuple(h.shape)}, output {tuple(y.shape)}, weights {w_post.numel()}")
+        mode = 1 if w_pre is not None else 2 if cast else 0
+        x = torch.empty((n, hidden), dtype=self.dtype, device=self.device) if mode else None
+        self._check(self.lib.idm_post_pre_norm(_p(h), _p(y), _p(w_post), eps, _p(w_pre), eps_pre, _p(x), mode, n,
+                                               hidden, self._stream()))
+        return x
+
+    def gated_act(self, gu: torch.Tensor, act: int) -> torch.Tensor:
+        """``act(gate) * up`` of a 32-bit gate/up product ``[N, 2 * inter]`` (gate columns, then up columns);
+        ``act``: 0 silu, 1 gelu (tanh form)."""
+        self._need(gu, torch.float32, "gate-up")
+        n, width = gu.shape
+        y = torch.empty((n, width // 2), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_gated_act(_p(gu), _p(y), n, width // 2, act, self._stream()))
+        return y
+
+    def token_gate(self, s, tokens, table, col0: int, act: int) -> torch.Tensor:
+        """``act(s[t]) * table[tokens[t], col0 : col0 + dim]`` in the storage dtype ``[N, dim]``."""
+        self._need(s, torch.float32, "token gate input")
+        self._need(table, self.dtype, "token table")
+        n, dim = s.shape
+        y = torch.empty((n, dim), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_token_gate(_p(s), _p(tokens), _p(table), table.shape[1], col0, _p(y), n, dim, act,
+                                            self._stream()))
+        return y
+
+    @staticmethod
+    def _state_stride(state: Optional[torch.Tensor]) -> int:
+        """Floats between two slots' regions of a per-sequence state ``[max_seqs, n]`` (a view of a wider one)."""
+        if state is None:
+            return 0
+        if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1:
+            raise KernelError("per-sequence state must be a 32-bit [slots, n] view with unit inner stride")
+        return state.stride(0)
+
+    def short_conv(self, proj, col0: int, channels: int, w, bias, act: int, state, ctx) -> torch.Tensor:
+        """Causal filter over time of columns ``[col0, col0 + channels)`` of the 32-bit ``proj [N, width]``; returns
+        32-bit ``[N, channels]``.  ``state [slots, (taps - 1) * channels]`` holds each sequence's last inputs."""
+        self._need(proj, torch.float32, "projection")
+        n, width = proj.shape
+        taps = w.shape[1]
+        out = torch.empty((n, channels), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_short_conv(_p(proj), width, col0, channels, taps, _p(w), _p(bias), act, _p(state),
+                                            self._state_stride(state), _p(out), _p(ctx.token_seq), _p(ctx.positions),
+                                            _p(ctx.slots), _p(ctx.q_start), _p(ctx.cu_q), n, self._stream()))
+        return out
+
+    def conv_qkv_cache(self, proj, col0: int, w, state, n_q, n_kv, dk, dv, cs, kv, ctx) -> torch.Tensor:
+        """q, k, v channels of ``proj`` filtered, q and k turned by the rotary table ``cs [N, half, 2]`` (or None),
+        k and v written to the cache entry; returns q ``[N, n_q, dk]``."""
+        self._need(proj, torch.float32, "projection")
+        n, width = proj.shape
+        half = 0 if cs is None else cs.shape[1]
+        if cs is not None and (cs.shape[0] != n or cs.dtype != torch.float32):
+            raise KernelError(f"rotary table {tuple(cs.shape)} does not match {n} tokens")
+        self._check_kv(kv, n_kv, dk, dv)
+        q = torch.empty((n, n_q, dk), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_conv_qkv_cache(_p(proj), width, col0, w.shape[1], _p(w), _p(state),
+                                                self._state_stride(state), n_q, n_kv, dk, dv, half, _p(cs), _p(q),
+                                                _p(kv.k), _p(kv.v), _p(kv.table), kv.table.shape[1],
+                                                _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), _p(ctx.q_start),
+                                                _p(ctx.cu_q), n, self._stream()))
+        return q
+
+    def conv_state_update(self, proj, col0: int, channels: int, taps: int, state, ctx) -> None:
+        """After a step of several tokens per sequence: the filter's state becomes each sequence's last inputs."""
+        if taps <= 1:
+            return
+        self._check(self.lib.idm_conv_state_update(_p(proj), proj.shape[1], col0, channels, taps, _p(state),
+                                                   self._state_stride(state), _p(ctx.slots), _p(ctx.q_start),
+                                                   _p(ctx.cu_q), _p(ctx.kv_len), ctx.n_seqs, self._stream()))
+
+    def ssd_scan(self, xbc, cols, proj, z_col: int, dt_col: int, dt_bias, a_log, d_skip, state, ctx, heads, groups,
+                 P, N) -> torch.Tensor:
+        """The state-space recurrence over the step's tokens, sequence by sequence; returns the gated output
+        ``y * silu(z)`` in 32-bit ``[N_tok, heads * P]`` and moves ``state [slots, heads * N * P]`` on."""
+        self._need(xbc, torch.float32, "filtered projection")
+        self._need(proj, torch.float32, "projection")
+        n = xbc.shape[0]
+        y = torch.empty((n, heads * P), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_ssd_scan(_p(xbc), xbc.shape[1], cols[0], cols[1], cols[2], _p(proj), proj.shape[1],
+                                          z_col, dt_col, _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
+                                          self._state_stride(state), _p(y), heads * P, _p(ctx.cu_q), _p(ctx.slots),
+                                          ctx.n_seqs, heads, groups, P, N, self._stream()))
+        return y
+
+    def ssd_group_norm(self, y, parts: int, w, eps: float, scale: float, out, out_col: int) -> None:
+        """``out[:, out_col : out_col + width] = rmsnorm over each of `parts` equal parts of y * w * scale``."""
+        self._need(y, torch.float32, "gated output")
+        self._need(out, self.dtype, "norm output")
+        n, width = y.shape
+        self._check(self.lib.idm_ssd_group_norm(_p(y), width, parts, _p(w), eps, float(scale), _p(out), out.shape[1],
+                                                out_col, n, self._stream()))
+
+    def attention_sink(self, q, kv, ctx, scale: float, sink, gate, gate_stride: int, out, out_col: int,
+                       out_scale: float) -> None:
+        """Causal attention over the cache entry with a sink per head (or None) and a sigmoid gate (a 32-bit view
+        ``[N, n_q * dv]`` with row stride ``gate_stride``, or None); the result times ``out_scale`` goes to
+        ``out[:, out_col : out_col + n_q * dv]``."""
+        self._need(q, self.dtype, "q")
+        self._need(out, self.dtype, "attention output")
+        n, n_q, dk = q.shape
+        dv = kv.v_head_dim
+        self._check_kv(kv, kv.n_kv_heads, dk, dv)
+        self._check(self.lib.idm_attention_sink(
+            _p(q), _p(out), out.shape[1], out_col, float(out_scale), _p(kv.k), _p(kv.v), _p(kv.table),
+            kv.table.shape[1], _p(sink), (gate.data_ptr() if gate is not None else None), gate_stride,
+            _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), _p(ctx.q_start), _p(ctx.cu_q), n, n_q,
+            kv.n_kv_heads, dk, dv, scale, 0, self._stream()))
+
+    def gemm_gated(self, x, w_tiled, inter: int, act: int) -> torch.Tensor:
+        """``act(x . gate^T) * (x . up^T)`` in the storage dtype ``[M, inter]`` (``tile_gate_up`` layout)."""
+        M, N, Kd = self._gemm_shape(x, w_tiled)
+        if N != -(-inter // 64) * 128:
+            raise KernelError(f"tiled gate/up weight has {N} rows, expected {-(-inter // 64) * 128}")
+        y = torch.empty((M, inter), dtype=self.dtype, device=self.device)
+        if M:
+            self._check(self.lib.idm_gemm_bf16_gated(_p(x), _p(w_tiled), _p(y), M, inter, Kd, act, self._stream()))
+        return y
+
     def add_rmsnorm(self, h, delta, gamma, eps: float, rows=None) -> torch.Tensor:
         self._need(h, torch.float32, "residual stream")
         self._need(gamma, torch.float32, "norm weight")
@@ -261,10 +408,14 @@ class Kernels:
             _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), self._stream()))
         return q, k_new, v_new
 
-    def _check_kv(self, kv, n_kv, hd):
+    def _check_kv(self, kv, n_kv, hd, v_hd=None):
         if kv.k.dtype != self.dtype or kv.k.shape[1:] != (n_kv, self.page, hd) or not kv.k.is_contiguous():
             raise KernelError(f"cache entry {tuple(kv.k.shape)} {kv.k.dtype} does not fit "
                               f"[pages, {n_kv}, {self.page}, {hd}] {self.dtype}")
+        v_hd = hd if v_hd is None else v_hd
+        if kv.v.dtype != self.dtype or kv.v.shape[1:] != (n_kv, self.page, v_hd) or not kv.v.is_contiguous():
+            raise KernelError(f"cache entry's values {tuple(kv.v.shape)} {kv.v.dtype} do not fit "
+                              f"[pages, {n_kv}, {self.page}, {v_hd}] {self.dtype}")
 
     def kv_write_ring(self, k_new, v_new, kv, ctx) -> None:
         n, n_kv, hd = k_new.shape

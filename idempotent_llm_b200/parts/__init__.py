@@ -7,7 +7,11 @@ from .rotary import Rotary
 from .attention import GQAAttention
 from .mlp import GatedMLP
 from .block import PreNormBlock
+from .sink_attention import SinkAttention
+from .ssd import SSDMixer
+from .parallel import ParallelMixer
+from .sandwich import SandwichBlock, TokenSide
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "FeedForward", "Mixer",
            "Norm", "Part", "PositionEncoding", "Runtime", "RMSNorm", "Rotary", "GQAAttention",
-           "GatedMLP", "PreNormBlock"]
+           "GatedMLP", "PreNormBlock", "SinkAttention", "SSDMixer", "ParallelMixer", "SandwichBlock", "TokenSide"]

@@ -43,7 +43,7 @@ the consumer adds them in ascending order.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List
 
 import torch
@@ -57,6 +57,15 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype          # compute/storage dtype of activations, weights and cache
     kernels: object             # idempotent_llm_b200.kernels.Kernels (or a stand-in with its methods)
+    shared: dict = field(default_factory=dict)   # what several parts of one model hold in common (a table cast once)
+
+    def shared_tensor(self, weights, name: str, dtype) -> "torch.Tensor":
+        """``weights[name]`` in ``dtype``, converted once however many parts ask for it."""
+        key = (name, dtype)
+        t = self.shared.get(key)
+        if t is None:
+            t = self.shared[key] = weights[name].to(dtype).contiguous()
+        return t
 
 
 class Part:

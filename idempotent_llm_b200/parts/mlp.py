@@ -11,6 +11,10 @@ from ..weights.loader import TensorDecl
 from .base import FEED_FORWARDS, FeedForward
 
 
+# the kernels' numbers of the gated activations (csrc/common.cuh: gated_act)
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(FeedForward):
     accepts_residual = True
@@ -23,8 +27,9 @@ class GatedMLP(FeedForward):
                 TensorDecl(prefix + nm.down, (spec.hidden, spec.intermediate))]
 
     def __init__(self, spec, weights, prefix, rt):
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not built; only 'silu'")
+        if spec.activation not in ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not built; known: {sorted(ACTIVATIONS)}")
+        self.act = ACTIVATIONS[spec.activation]
         self.spec = spec
         self.rt = rt
         nm = spec.names
@@ -44,8 +49,8 @@ class GatedMLP(FeedForward):
     def emit(self, prog, x, h):
         """The calls of ``forward`` on the fused path, adding into the stream ``h``."""
         from ..kernels.program import NotProgrammable
-        if not self.fused:
-            raise NotProgrammable("the activation as a kernel of its own is called from forward")
+        if not self.fused or self.act != 0:
+            raise NotProgrammable("the activation as a kernel of its own, or another than silu, is called from forward")
         s = self.spec
         y = prog.buffer("feed_forward.y", per_token=2 * s.intermediate)
         prog.gemm_swiglu(x, self.w_gate_up, s.hidden, s.intermediate, y)
@@ -55,11 +60,12 @@ class GatedMLP(FeedForward):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         K = self.rt.kernels
         if self.fused:
-            y = K.gemm_swiglu(x, self.w_gate_up, self.spec.intermediate)
+            y = (K.gemm_swiglu(x, self.w_gate_up, self.spec.intermediate) if self.act == 0
+                 else K.gemm_gated(x, self.w_gate_up, self.spec.intermediate, self.act))
             if residual is not None:
                 K.gemm_residual(y, self.w_down, residual)
                 return None
             return K.gemm(y, self.w_down)
         gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate]
-        y = K.swiglu(gu)                        # [N, intermediate]
+        y = K.swiglu(gu) if self.act == 0 else K.gated_act(gu[0], self.act)      # [N, intermediate]
         return K.gemm(y, self.w_down)           # [P, N, hidden]

@@ -10,9 +10,25 @@ the mixer's kernel.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import POSITIONS, PositionEncoding
+
+
+def frequencies(spec) -> torch.Tensor:
+    """``theta ** (-2 j / dim)`` for ``j < dim / 2`` in 64-bit, then the spec's scaling by wavelength, if any
+    (``WavelengthScaling``: short waves kept, long waves divided by the factor, a linear blend between)."""
+    j = torch.arange(0, spec.dim // 2, dtype=torch.float64)
+    f = float(spec.theta) ** (-2.0 * j / spec.dim)
+    sc = getattr(spec, "scaling", None)
+    if sc is None:
+        return f
+    wave = 2.0 * math.pi / f
+    s = (sc.original / wave - sc.low) / (sc.high - sc.low)
+    blend = (1.0 - s) * f / sc.factor + s * f
+    return torch.where(wave < sc.original / sc.high, f, torch.where(wave > sc.original / sc.low, f / sc.factor, blend))
 
 
 @POSITIONS.register("rotary")
@@ -22,12 +38,13 @@ class Rotary(PositionEncoding):
             raise ValueError(f"rotary dimension {spec.dim} must be even")
         self.spec = spec
         self.rt = rt
-        j = torch.arange(0, spec.dim // 2, dtype=torch.float64)
-        self.inv_freq = (float(spec.theta) ** (-2.0 * j / spec.dim)).to(rt.device)
+        self.inv_freq = frequencies(spec).to(rt.device)
+        sc = getattr(spec, "scaling", None)
+        self._key = ("rotary", float(spec.theta), spec.dim, None if sc is None else (sc.factor, sc.low, sc.high, sc.original))
 
     def emit(self, prog):
         """The table's two buffers in a step program (made once a step, like ``tables``)."""
-        key = ("rotary", float(self.spec.theta), self.spec.dim)
+        key = self._key
         bufs = prog.shared.get(key)
         if bufs is None:
             per_token = self.spec.dim // 2 * 2 * 4
@@ -37,7 +54,7 @@ class Rotary(PositionEncoding):
         return bufs
 
     def tables(self, ctx):
-        key = ("rotary", float(self.spec.theta), self.spec.dim)
+        key = self._key
         t = ctx.memo.get(key)
         if t is None:
             t = self.rt.kernels.rope_table(ctx.positions, self.inv_freq)

@@ -55,16 +55,26 @@ def read_config(model_dir: str):
         raise ConfigError(f"{path} does not exist")
     with open(path) as f:
         raw = json.load(f)
-    archs = raw.get("architectures")
-    if not archs:
-        raise ConfigError(f"{path}: key 'architectures' is missing or empty")
-    arch = architecture(archs[0])
+    arch = architecture(architecture_name(raw, path))
     return arch, arch.config_class.from_dict(raw)
+
+
+def architecture_name(raw: dict, where: str = "config.json") -> str:
+    """The name a config.json gives its architecture: the first of ``architectures`` (a list), or
+    ``architecture`` (one name)."""
+    archs = raw.get("architectures")
+    if archs:
+        return archs[0]
+    if isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
+    raise ConfigError(f"{where}: key 'architectures' (or 'architecture') is missing or empty")
 
 
 def _register_builtin() -> None:
     from .config.qwen3 import ARCHITECTURE, Qwen3Config
     register_architecture(ARCHITECTURE, Qwen3Config)
+    from .config.lunulix import ARCHITECTURE as LUNULIX, LunulixConfig
+    register_architecture(LUNULIX, LunulixConfig)
 
 
 _register_builtin()

@@ -27,7 +27,8 @@ from .safetensors_io import SafetensorsDir
 @dataclass(frozen=True)
 class TensorDecl:
     """A tensor a part needs: checkpoint name, shape, and how random init draws it
-    (``normal``: N(0, std); ``one_plus_normal``: 1 + N(0, std), for norm weights)."""
+    (``normal``: N(0, std); ``one_plus_normal``: 1 + N(0, std), for norm weights; ``filter`` and
+    ``unit_normal``: N(0, 0.5), for a short filter's taps and per-head constants)."""
 
     name: str
     shape: Tuple[int, ...]

@@ -26,10 +26,14 @@ def _tensor_seed(seed: int, name: str) -> int:
 def draw(decl: TensorDecl, seed: int, std: float, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, decl.name))
-    t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * std
+    t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init in ("filter", "unit_normal"):
+        t = t * 0.5             # taps of a short filter, per-head constants: of order one whatever `std` is
+    else:
+        t = t * std
     if decl.init == "one_plus_normal":
         t = t + 1.0
-    elif decl.init != "normal":
+    elif decl.init not in ("normal", "filter", "unit_normal"):
         raise ValueError(f"unknown init {decl.init!r} for {decl.name}")
     return t.to(dtype)
 
