@@ -95,3 +95,71 @@ def run_trace(model_dir: str, dtype: str, steps: list, out_dir: str, max_tokens:
         else:
             assert not os.path.exists(path)
     return out
+
+
+# ------------------------------------------------------------------------------------- Lunulix
+def lunulix_layer(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.3, lconv=3, rot_dims=8, rot_base=5000.0,
+                  scaling=(4.0, 1.0, 4.0, 64), r_heads=3, r_vdim=8, state=12, groups=1, rconv=4, norm_groups=2,
+                  left_scale=0.7, right_scale=1.3, ff=40):
+    """One layer of a Lunulix config.json; every size and constant is an argument."""
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale)
+    if lconv:
+        left["conv"] = lconv
+    if rot_dims:
+        left["rot"] = dict(base=rot_base, dims=rot_dims)
+        if scaling:
+            left["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    right = dict(heads=r_heads, vdim=r_vdim, state=state, groups=groups, conv=rconv, norm_groups=norm_groups)
+    return dict(type="parallel", mixer=dict(left=left, right=right, left_scale=left_scale, right_scale=right_scale),
+                mlp=None if not ff else dict(kind="dense", ff=ff))
+
+
+def lunulix_config(layers, vocab=97, width=32, emb_scale=3.0, eps=1e-5, side_dim=8):
+    d = dict(architecture="Lunulix", vocab=vocab, width=width, embedding=dict(scale=emb_scale), norm=dict(eps=eps),
+             layers=list(layers))
+    if side_dim:
+        d["token_side"] = dict(dim=side_dim)
+    return d
+
+
+# Small Lunulix models that differ from one another in every size and option.
+LUNULIX = {
+    # two unlike layers: grouped heads with key and value rows of different widths, a partial rotation with scaled
+    # frequencies, filters of 3 and 4 taps; then a layer without feed-forward, whole-head rotation without scaling,
+    # other filters, one norm part, state size no multiple of 4
+    "P": lambda: lunulix_config([
+        lunulix_layer(),
+        lunulix_layer(heads=2, kv_heads=2, dim=24, vdim=16, scale=0.2, lconv=2, rot_dims=24, scaling=None, r_heads=4,
+                      r_vdim=12, state=10, groups=2, rconv=3, norm_groups=1, left_scale=1.0, right_scale=0.5, ff=None)]),
+    # no token side input, no embedding scale, no filter and no rotation on the attention side, one kv-head,
+    # norm parts that cut through heads (3 heads of 8 in 4 parts of 6)
+    "Q": lambda: lunulix_config([
+        lunulix_layer(heads=3, kv_heads=1, dim=8, vdim=8, lconv=0, rot_dims=0, r_heads=3, r_vdim=8, state=16, groups=3,
+                      rconv=2, norm_groups=4, ff=24)], vocab=50, width=24, emb_scale=1.0, side_dim=0),
+    # head sizes the tensor-core attention has (64), three layers, width 64
+    "R": lambda: lunulix_config([lunulix_layer(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.125, rot_dims=32,
+                                               r_heads=2, r_vdim=32, state=32, groups=1, ff=96)] * 3,
+                                vocab=211, width=64, emb_scale=8.0, side_dim=16),
+}
+
+
+def make_lunulix_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.15, edit=None) -> str:
+    """A Lunulix model folder with seeded random weights; ``edit(name, tensor) -> tensor`` may change them."""
+    from idempotent_llm_b200.config import LunulixConfig
+    from idempotent_llm_b200.weights import write_random_model, write_safetensors, SafetensorsFile
+    write_random_model(LunulixConfig.from_dict(cfg), out_dir, seed=seed, dtype=dtype, std=std)
+    if edit is not None:
+        path = os.path.join(out_dir, "model.safetensors")
+        f = SafetensorsFile(path)
+        tensors = [(n, edit(n, f.get(n).clone())) for n in f.names()]
+        del f
+        write_safetensors(path, tensors)
+    return out_dir
+
+
+def read_lunulix(model_dir: str):
+    """(config dict, tensors by name) read without the package (for the plain implementation)."""
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(model_dir, "model.safetensors"))
