@@ -119,8 +119,14 @@ def headline_lengths(batch: int, context: int, reserve: int, seed: int):
 
 
 def kv_bytes_per_token(eng) -> int:
-    return sum(2 * g_.need.n_kv_heads * g_.need.head_dim * g_.k.element_size() * len(g_.entries)
+    import math
+    return sum((math.prod(g_.need.key_row()) + math.prod(g_.need.value_row())) * g_.k.element_size() * len(g_.entries)
                for g_ in eng.cache.groups)
+
+
+def state_bytes_per_sequence(eng) -> int:
+    """Per-sequence state of fixed size (a recurrent mixer's), which a decode step reads and writes."""
+    return sum(st[0].numel() * st.element_size() for st in eng.cache.state.values())
 
 
 def decode_point(lm, lens, steps: int, warmup: int, seed: int, repeats: int = 1, sampler=None):
@@ -155,7 +161,7 @@ def decode_point(lm, lens, steps: int, warmup: int, seed: int, repeats: int = 1,
     ms = statistics.median(times)
     sess.finish()
     mean_len = sum(l + warmup + repeats * steps / 2 for l in lens)
-    bytes_step = lm.model.weight_bytes() + kv_bytes_per_token(eng) * mean_len
+    bytes_step = lm.model.weight_bytes() + kv_bytes_per_token(eng) * mean_len + 2 * batch * state_bytes_per_sequence(eng)
     toks = sess.tokens()
     assert toks.shape == (total, batch) and int(toks.min()) >= 0 and int(toks.max()) < V
     for s in slots:
@@ -197,9 +203,27 @@ def e2e_point(lm, lens, steps: int, warmup: int, seed: int):
     return batch * steps / dt, (8 * batch + 1 + 1) // 2 * 2 * 4, batch * 4
 
 
+def lunulix_prefill_flops(cfg, lens) -> float:
+    """The same count for a Lunulix configuration: per layer the joint input projection, the joint output
+    projection, the feed-forward and the token side input; causal attention with key and value rows of their own
+    widths; the recurrence (per token, head, state element and column: decay, outer product, read-out)."""
+    W, tokens, total = cfg.width, sum(lens), 0.0
+    for L in cfg.layers:
+        l, r = L.left, L.right
+        inner_l, inner_r = l.heads * l.vdim, r.heads * r.vdim
+        rows_in = (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim + inner_l + 2 * inner_r + 2 * r.groups * r.state + r.heads
+        linear = W * rows_in + (inner_l + inner_r) * W + (3 * W * L.ff if L.ff else 0) + 2 * W * (cfg.token_side_dim or 0)
+        total += 2 * tokens * linear
+        total += sum(l.heads * 2 * (l.dim + l.vdim) * t * (t + 1) // 2 for t in lens)
+        total += 6 * tokens * r.heads * r.vdim * r.state
+    return total + 2 * W * cfg.vocab * len(lens)
+
+
 def prefill_flops(cfg, lens) -> float:
     """Multiply-adds x 2 of a step that brings whole prompts of ``lens`` tokens: the layers' products, causal
     attention, and the head at each prompt's last position."""
+    if hasattr(cfg, "layers") and not hasattr(cfg, "hidden_size"):
+        return lunulix_prefill_flops(cfg, lens)
     H, L, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size
     qd, kd = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
     tokens = sum(lens)
@@ -306,6 +330,135 @@ def check_cuts_bitwise(lm, seed: int = 0):
     return bool(same)
 
 
+def kernel_times(lm, lens, seed: int):
+    """Device time of every kernel wrapper (``Kernels`` method) over one step, each call between two CUDA events
+    and a synchronize, after an untimed step of the same shape: {method: (calls, ms in all)}.  The step runs
+    call by call (no step program, no graph), so the sum is not the step's time; it says where the time goes."""
+    import torch
+    eng, K = lm.engine, lm.model.rt.kernels
+    V = lm.config.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    names = [n for n in dir(K) if not n.startswith("_") and callable(getattr(K, n)) and n not in
+             ("scratch", "attention_tc_plan", "attention_tc_status", "gemm_status", "gemm_choices", "attention_tc_few_rows",
+              "tile_gate_up", "attention", "gemm", "wait_probe", "sample")]
+    out, saved = {}, {n: getattr(K, n) for n in names}
+    timing = [False]
+
+    def wrap(name, fn):
+        def call(*a, **k):
+            if not timing[0]:
+                return fn(*a, **k)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            r = fn(*a, **k)
+            t1.record()
+            torch.cuda.synchronize()
+            c, ms = out.get(name, (0, 0.0))
+            out[name] = (c + 1, ms + t0.elapsed_time(t1))
+            return r
+        return call
+    programs, graphs = getattr(K, "use_programs", False), eng.use_graph
+    K.use_programs, eng.use_graph = False, False
+    try:
+        for n in names:
+            setattr(K, n, wrap(n, saved[n]))
+        for timed in (False, True):
+            timing[0] = timed
+            slots = [eng.open() for _ in lens]
+            ids = [torch.randint(min(100, V - 1), min(50000, V), (n,), generator=g).tolist() for n in lens]
+            eng.step(list(zip(slots, ids)))
+            for s in slots:
+                eng.close(s)
+    finally:
+        for n in names:
+            setattr(K, n, saved[n])
+        K.use_programs, eng.use_graph = programs, graphs
+    return {n: {"calls": c, "ms": round(ms, 4)} for n, (c, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def decode_kernel_times(lm, lens, seed: int):
+    """The same for one single-token step of a batch whose sequences already hold ``lens`` tokens."""
+    import torch
+    eng = lm.engine
+    V = lm.config.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    slots = [eng.open() for _ in lens]
+    for s_, n in zip(slots, lens):
+        eng.step([(s_, torch.randint(min(100, V - 1), min(50000, V), (n,), generator=g).tolist())])
+    K = lm.model.rt.kernels
+    names = ["embed", "embed_scaled", "add_rmsnorm", "post_pre_norm", "rope_table", "gemm_store", "gemm_residual", "gemm_swiglu",
+             "gemm_gated", "gemm_qkv", "attention_tc", "attention_generic", "attention_sink", "conv_qkv_cache", "short_conv",
+             "ssd_scan", "ssd_group_norm", "token_gate", "gated_act", "attention_lse_gate"]
+    names = [n for n in names if hasattr(K, n)]
+    out, saved = {}, {n: getattr(K, n) for n in names}
+    timing = [False]
+
+    def wrap(name, fn):
+        def call(*a, **k):
+            if not timing[0]:
+                return fn(*a, **k)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            r = fn(*a, **k)
+            t1.record()
+            torch.cuda.synchronize()
+            c, ms = out.get(name, (0, 0.0))
+            out[name] = (c + 1, ms + t0.elapsed_time(t1))
+            return r
+        return call
+    programs, graphs = getattr(K, "use_programs", False), eng.use_graph
+    K.use_programs, eng.use_graph = False, False
+    try:
+        for n in names:
+            setattr(K, n, wrap(n, saved[n]))
+        for timed in (False, True):
+            timing[0] = timed
+            eng.step([(s_, [5]) for s_ in slots])
+    finally:
+        for n in names:
+            setattr(K, n, saved[n])
+        K.use_programs, eng.use_graph = programs, graphs
+        for s_ in slots:
+            eng.close(s_)
+    return {n: {"calls": c, "ms": round(ms, 4)} for n, (c, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def design_comparison(args) -> int:
+    """``--design lunulix``: decode and prefill throughput of the Lunulix design beside Qwen3 at equal width, depth,
+    heads, feed-forward size and vocabulary (random weights), with where a step's time goes kernel by kernel."""
+    import torch
+    import idempotent_llm_b200 as idm
+    from idempotent_llm_b200.config.presets import preset
+    pk = peaks()
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    sizes = [s for s in args.design_sizes.split(",") if s]
+    steps = min(args.steps, 32)
+    rows = {}
+    for size in sizes:
+        for arch in ("qwen3", args.design):
+            cfg = preset(f"{arch}-{size}")
+            lm = idm.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2304, max_seqs=64, max_seq_len=2304)
+            r = {"params_b": lm.model.weight_bytes() / 2e9}
+            for b, seed in ((1, 11), (8, 12), (64, 13)):
+                d = decode_point(lm, prompt_lengths(b, 128, 2048, seed), steps, max(args.warmup, 3), seed, 3)
+                r[f"decode_b{b}_tok_s"], r[f"decode_b{b}_ms"] = d["tps"], d["ms"]
+                r[f"decode_b{b}_hbm_frac"] = d["bytes"] / (d["ms"] * 1e-3) / hbm
+                r[f"decode_b{b}_launches"] = d["launches"]
+            for lens, key in (([2048], "prefill_2048"), (prompt_lengths(8, 128, 2048, 14), "prefill_8_prompts")):
+                t, ms, fl = prefill_point(lm, lens, 2, 3, 14)
+                r[key + "_tok_s"], r[key + "_ms"], r[key + "_frac"] = t, ms, fl / (ms * 1e-3) / tf
+            r["kernels_prefill_2048"] = kernel_times(lm, [2048], 5)
+            r["kernels_decode_b8"] = decode_kernel_times(lm, [1500] * 8, 6)
+            rows[f"{arch}-{size}"] = r
+            del lm
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": f"decode and prefill of {args.design} beside qwen3 at equal sizes (bf16, random weights)",
+                      "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
+                      "data": "synthetic: seeded random weights and uniform-random token ids", "peaks": pk,
+                      "rows": rows}))
+    return 0
+
+
 def reference_arm(args) -> int:
     """The unmodified reference on the same configuration: ``baseline/reference_arm.py``."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -328,6 +481,9 @@ def main() -> int:
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median counts")
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the 32-bit check")
     ap.add_argument("--skip-sizes", action="store_true", help="leave out the points at 8B and 32B layer sizes")
+    ap.add_argument("--design", default="", choices=["", "lunulix"],
+                    help="instead of the default workload: this design beside qwen3 at equal layer sizes")
+    ap.add_argument("--design-sizes", default="0.6b,8b", help="layer sizes of --design (presets <design>-<size>)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this library runs on one device)")
@@ -335,6 +491,8 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        return design_comparison(args)
 
     import torch
     import idempotent_llm_b200 as idm

@@ -597,13 +597,15 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 if (r >= rv) continue;
                 float M = -INFINITY, L = 0.f, a_, b_;
                 fold_coeffs(M, L, mfin_sm[r], lfin_sm[r], a_, b_);
+                const float sa = a.sink ? fold_sink(a.sink, head0 + (r & (gp - 1)), M, L) : 1.0f;
                 const float inv = __fdiv_rn(1.0f, L);
                 T* orow = a.out + ((size_t)(tok0 + (r >> gs)) * a.n_q + head0 + (r & (gp - 1))) * HD;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const int dd = d_warp + nt * 8 + tig * 2;
-                    const __nv_bfloat162 pk = __floats2bfloat162_rn(__fmul_rn(fold_value(0.f, a_, o[nt][2 * half], b_), inv),
-                                                                    __fmul_rn(fold_value(0.f, a_, o[nt][2 * half + 1], b_), inv));
+                    float o0 = fold_value(0.f, a_, o[nt][2 * half], b_), o1 = fold_value(0.f, a_, o[nt][2 * half + 1], b_);
+                    if (a.sink) { o0 = __fmul_rn(o0, sa); o1 = __fmul_rn(o1, sa); }
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(__fmul_rn(o0, inv), __fmul_rn(o1, inv));
                     *reinterpret_cast<__nv_bfloat162*>(orow + dd) = pk;
                 }
             }

@@ -70,6 +70,8 @@ __device__ __forceinline__ void attn_item_stamp(int, int) {}
 
 struct AttnTcArgs {
     T* out;
+    const float* sink;                                 // [n_q] or null: a learned score per head (natural units, not scaled) that joins
+                                                       // the softmax's sum with no key and no value
     const int* tile_seq; const int* tile_start;
     const int* cu_q; const int* q_start; const int* kv_len; const int* slots;
     const int* table; int table_stride;
@@ -115,6 +117,15 @@ __device__ __forceinline__ void fold_coeffs(float& M, float& L, float m, float l
 }
 __device__ __forceinline__ float fold_value(float o_tot, float a_, float o_run, float b_) {
     return __fmaf_rn(o_tot, a_, __fmul_rn(o_run, b_));
+}
+
+// A sink is folded like one more run behind the last: score sink[head], sum 1, no context.  Returns what the
+// context is scaled by (M, L move on); every kernel and every way through scratch folds it at this one place,
+// after all runs of keys, so the bits do not depend on which of them ran.
+__device__ __forceinline__ float fold_sink(const float* sink, int head, float& M, float& L) {
+    float a_, b_;
+    fold_coeffs(M, L, __fmul_rn(sink[head], 1.4426950408889634f), 1.0f, a_, b_);
+    return a_;
 }
 
 // 16 finished values of a row as bfloat16: 32 bytes, two stores
@@ -167,6 +178,10 @@ __device__ __forceinline__ void fold_runs_and_store(const AttnTcArgs& a, const f
                 }
             }
         }
+        if (a.sink) {
+            const float sa = fold_sink(a.sink, head0 + (row & (gp - 1)), M, L);
+            acc.x = __fmul_rn(acc.x, sa); acc.y = __fmul_rn(acc.y, sa);
+        }
         const float inv = __fdiv_rn(1.0f, L);
         T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4 + 2 * half;
         *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
@@ -213,6 +228,11 @@ __device__ __forceinline__ void fold_rows_and_store(const AttnTcArgs& a, const f
                     }
                 }
             }
+        }
+        if (a.sink) {
+            const float sa = fold_sink(a.sink, head0 + (r & (gp - 1)), M, L);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = __fmul_rn(acc[i], sa);
         }
         store_out16(dst + c, acc, __fdiv_rn(1.0f, L));
     }
@@ -603,6 +623,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             float a_, b_;
             const bool first = tot == nullptr;
             fold_coeffs(M_tot, L_tot, m_ref, l, a_, b_);
+            const float sa = (a.sink && row_live) ? fold_sink(a.sink, head0 + (r & (gp - 1)), M_tot, L_tot) : 1.0f;
             const float inv = __fdiv_rn(1.0f, L_tot);
             const float4* mine = reinterpret_cast<const float4*>(tot);
 #pragma unroll 1
@@ -616,6 +637,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         if (!first) t = mine[(c / 4 + k) * AP_BM + r];
                         o[4 * k] = fold_value(t.x, a_, o[4 * k], b_); o[4 * k + 1] = fold_value(t.y, a_, o[4 * k + 1], b_);
                         o[4 * k + 2] = fold_value(t.z, a_, o[4 * k + 2], b_); o[4 * k + 3] = fold_value(t.w, a_, o[4 * k + 3], b_);
+                    }
+                    if (a.sink) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = __fmul_rn(o[i], sa);
                     }
                     store_out16(orow + c, o, inv);
                 }
@@ -674,12 +699,12 @@ extern "C" long long idm_attention_tc_scratch_floats(int n_tiles, int n_q, int n
 // 128 / heads_per_tile tokens, longest first; rows_cap: the most rows (tokens x heads_per_tile) any tile has.  max_runs > 0: every run of `run_blocks` key blocks is a
 // block of its own and results meet in scratch; max_runs == 0:
 // one block per tile and head group (`scratch` may be null if no tile has more than run_blocks key blocks).
-extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, const void* v_pool, int n_pages,
-                                const int* table, int table_stride, const int* tile_seq, const int* tile_start,
-                                int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
-                                const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
-                                int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
-                                int max_parts, int runs_per_part, cudaStream_t stream) {
+static int attention_tc_any(const void* q, void* out, const float* sink, const void* k_pool, const void* v_pool, int n_pages,
+                            const int* table, int table_stride, const int* tile_seq, const int* tile_start,
+                            int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
+                            const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
+                            int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
+                            int max_parts, int runs_per_part, cudaStream_t stream) {
     // (tile_pool / max_parts / runs_per_part, with max_runs == 0: tiles whose entry in tile_pool is not -1 are shared
     // by up to max_parts blocks of runs_per_part runs each; their runs' results lie in the scratch behind the
     // one-context-per-tile region, from the slot tile_pool names on, head group after head group)
@@ -714,7 +739,7 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
         IDM_REQUIRE(r == 0, "attention_tc: tensor map for v failed (%d)", r);
     }
     AttnTcArgs a;
-    a.out = (T*)out; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
+    a.out = (T*)out; a.sink = sink; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
     a.kv_len = kv_len; a.slots = slots; a.table = table; a.table_stride = table_stride;
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
@@ -728,6 +753,30 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
                         : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);
     return hd == 64 ? launch_attention_tc<64>(mq, mk, mv, a, n_tiles, stream)
                     : launch_attention_tc<128>(mq, mk, mv, a, n_tiles, stream);
+}
+
+extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, const void* v_pool, int n_pages,
+                                const int* table, int table_stride, const int* tile_seq, const int* tile_start,
+                                int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
+                                const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
+                                int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
+                                int max_parts, int runs_per_part, cudaStream_t stream) {
+    return attention_tc_any(q, out, nullptr, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+                            q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
+                            tile_pool, max_parts, runs_per_part, stream);
+}
+
+// The same attention with a sink: a learned score per q-head (32-bit, natural units, not scaled) that joins the
+// softmax's sum with no key and no value.
+extern "C" int idm_attention_tc_sink(const void* q, void* out, const float* sink, const void* k_pool, const void* v_pool,
+                                     int n_pages, const int* table, int table_stride, const int* tile_seq,
+                                     const int* tile_start, int n_tiles, const int* cu_q, const int* q_start,
+                                     const int* kv_len, const int* slots, int n_tokens, int n_q, int n_kv, int hd,
+                                     float scale, int run_blocks, int max_runs, int rows_cap, float* scratch,
+                                     const int* tile_pool, int max_parts, int runs_per_part, cudaStream_t stream) {
+    return attention_tc_any(q, out, sink, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+                            q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
+                            tile_pool, max_parts, runs_per_part, stream);
 }
 
 // 0: tiles of few rows go through the tcgen05 kernel as well (tests compare the two bit for bit); returns the old setting

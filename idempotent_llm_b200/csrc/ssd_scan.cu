@@ -9,7 +9,9 @@
 // projection), z and the raw step sizes columns of another (the projection itself).  Head h reads group
 // h / (heads / groups).  One block owns (sequence, head, a slice of P) and walks the sequence's tokens of
 // this step in order; a thread keeps N / 4 state elements of one column p in registers, four threads
-// share a column and add their parts of y by shuffles in a fixed order.  A step of one token and a step
+// share a column and add their parts of y by shuffles in a fixed order.  B and C of a few tokens are staged in
+// shared memory, each thread's quarter of N in a row of its own, padded so that the four quarters read by a
+// warp in one 16-byte load fall into different banks.  A step of one token and a step
 // of a thousand run the same operations on the same numbers for every token.
 //
 // ssd_group_norm: the gated output in `parts` equal parts, each divided by its own root mean square,
@@ -17,8 +19,8 @@
 #include "common.cuh"
 
 #define SSD_NS 4            // threads per column of the state
-#define SSD_PB 32           // columns of the state per block
-#define SSD_CHUNK 8         // tokens staged in shared memory at a time
+#define SSD_PB 16           // columns of the state per block
+#define SSD_CHUNK 16        // tokens staged in shared memory at a time
 
 struct SsdArgs {
     const float* xbc; int xbc_stride; int x_col, b_col, c_col;    // filtered projection
@@ -36,16 +38,17 @@ template <int NPT>
 __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int s = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SSD_PB;
     const int g = h / (a.heads / a.groups);
     const int pl = threadIdx.x / SSD_NS, ns = threadIdx.x % SSD_NS;
     const int p = p0 + pl;
     const bool live = p < a.P;
     const int t0 = a.cu_q[s], t1 = a.cu_q[s + 1];
-    float* sB = sm;                              // [CHUNK][N]
-    float* sC = sB + SSD_CHUNK * a.N;            // [CHUNK][N]
-    float* sX = sC + SSD_CHUNK * a.N;            // [CHUNK][PB]
+    constexpr int ROW = NPT + 4;                 // a quarter of N, padded: the quarters' rows start 4 banks apart
+    float* sB = sm;                              // [CHUNK][4][ROW]
+    float* sC = sB + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][4][ROW]
+    float* sX = sC + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][PB]
     float* sZ = sX + SSD_CHUNK * SSD_PB;         // [CHUNK][PB]
     float* sDt = sZ + SSD_CHUNK * SSD_PB;        // [CHUNK] step sizes, [CHUNK] decays
     float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * a.N * a.P;
@@ -59,11 +62,12 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     for (int tc = t0; tc < t1; tc += SSD_CHUNK) {
         const int nt = min(SSD_CHUNK, t1 - tc);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * a.N; i += blockDim.x) {
-            const int tt = i / a.N, n = i % a.N;
+        for (int i = threadIdx.x; i < nt * SSD_NS * NPT; i += blockDim.x) {
+            const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
             const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride;
-            sB[tt * a.N + n] = row[a.b_col + g * a.N + n];
-            sC[tt * a.N + n] = row[a.c_col + g * a.N + n];
+            const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
+            sB[at] = n < a.N ? row[a.b_col + g * a.N + n] : 0.f;          // (zeros past N: those state elements stay zero)
+            sC[at] = n < a.N ? row[a.c_col + g * a.N + n] : 0.f;
         }
         for (int i = threadIdx.x; i < nt * SSD_PB; i += blockDim.x) {
             const int tt = i / SSD_PB, pp = p0 + i % SSD_PB;
@@ -81,15 +85,16 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
             const float dt = sDt[tt], decay = sDt[SSD_CHUNK + tt];
             const float x = sX[tt * SSD_PB + pl];
             const float dtx = dt * x;
-            const float* Bt = sB + tt * a.N + ns * NPT;
-            const float* Ct = sC + tt * a.N + ns * NPT;
+            const float4* Bt = reinterpret_cast<const float4*>(sB + (tt * SSD_NS + ns) * ROW);
+            const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                if (ns * NPT + i < a.N) {
-                    S[i] = fmaf(decay, S[i], dtx * Bt[i]);
-                    acc = fmaf(S[i], Ct[i], acc);
-                }
+            for (int i = 0; i < NPT / 4; ++i) {
+                const float4 b = Bt[i], c = Ct[i];
+                S[4 * i] = fmaf(decay, S[4 * i], dtx * b.x);         acc = fmaf(S[4 * i], c.x, acc);
+                S[4 * i + 1] = fmaf(decay, S[4 * i + 1], dtx * b.y); acc = fmaf(S[4 * i + 1], c.y, acc);
+                S[4 * i + 2] = fmaf(decay, S[4 * i + 2], dtx * b.z); acc = fmaf(S[4 * i + 2], c.z, acc);
+                S[4 * i + 3] = fmaf(decay, S[4 * i + 3], dtx * b.w); acc = fmaf(S[4 * i + 3], c.w, acc);
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
@@ -124,8 +129,9 @@ extern "C" int idm_ssd_scan(const float* xbc, int xbc_stride, int x_col, int b_c
     a.y = y; a.y_stride = y_stride; a.cu_q = cu_q; a.slots = slots;
     a.heads = heads; a.groups = groups; a.P = P; a.N = N;
     const dim3 grid(n_seqs, heads, (P + SSD_PB - 1) / SSD_PB), block(SSD_NS * SSD_PB);
-    const size_t smem = (size_t)(2 * SSD_CHUNK * N + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
     const int npt = (N + SSD_NS - 1) / SSD_NS;
+    const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
+    const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
     if (npt <= 8) idm_launch(ssd_scan_kernel<8>, grid, block, smem, stream, a);
     else if (npt <= 16) idm_launch(ssd_scan_kernel<16>, grid, block, smem, stream, a);
     else if (npt <= 32) idm_launch(ssd_scan_kernel<32>, grid, block, smem, stream, a);

@@ -87,6 +87,8 @@ SIGNATURES = {
     "idm_attention_tc_heads_per_tile": (c_int, "ii"),
     "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
     "idm_attention_tc": (c_int, "ppppipippippppiiiifiiippiip"),
+    "idm_attention_tc_sink": (c_int, "pppppipippippppiiiifiiippiip"),
+    "idm_gate_scale": (c_int, "ppifpiiiip"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_attention_tc_set_few_rows": (c_int, "i"),
     "idm_gemm_f32": (c_int, "pppiiip"),
@@ -441,7 +443,7 @@ class Kernels:
             return self.attention_tc(q, kv, ctx, scale)
         return self.attention_generic(q, kv, ctx, k_new, v_new, scale, window)
 
-    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None) -> torch.Tensor:
+    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None, sink=None) -> torch.Tensor:
         """Causal attention on the tensor cores: tiles of (128 / gp tokens) x (gp q-heads of one kv-head).
 
         Steps with few tokens per sequence (at most 32 rows a tile: single tokens above all) give every
@@ -454,13 +456,35 @@ class Kernels:
             out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
         (tile_seq, tile_start, n_tiles, rows_cap, max_runs, scratch, tile_pool, max_parts,
          per) = self.attention_tc_plan(ctx, n_q, kv.n_kv_heads, hd, through_scratch, share)
-        self._check(self.lib.idm_attention_tc(
-            _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
-            _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
-            _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
-            hd, scale, self.attention_run_blocks, max_runs, rows_cap, scratch, tile_pool, max_parts, per,
-            self._stream()))
+        rest = (_p(kv.k), _p(kv.v), kv.k.shape[0],
+                _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
+                _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
+                hd, scale, self.attention_run_blocks, max_runs, rows_cap, scratch, tile_pool, max_parts, per,
+                self._stream())
+        if sink is None:
+            self._check(self.lib.idm_attention_tc(_p(q), _p(out), *rest))
+        else:
+            # a learned score per q-head that joins the softmax's sum with no key and no value
+            self._need(sink, torch.float32, "sink")
+            if sink.numel() != n_q:
+                raise KernelError(f"{sink.numel()} sinks for {n_q} q-heads")
+            self._check(self.lib.idm_attention_tc_sink(_p(q), _p(out), _p(sink), *rest))
         return out
+
+    def attention_tc_fits(self, kv, hd: int, dv: int) -> bool:
+        """Whether the tensor-core attention has this layer: bfloat16, key and value rows of one width that it has
+        a kernel for, no ring."""
+        return (self.dtype == torch.bfloat16 and self.attention_impl == "tcgen05" and hd == dv and kv.ring == 0
+                and bool(self.lib.idm_attention_tc_supports(hd)))
+
+    def gate_scale(self, o, gate, gate_stride: int, scale: float, out, out_col: int) -> None:
+        """``out[:, out_col : out_col + width] = o * sigmoid(gate) * scale`` (``gate``: a 32-bit view with row stride
+        ``gate_stride``, or None for the constant alone)."""
+        self._need(o, self.dtype, "mixer output")
+        self._need(out, self.dtype, "gated output")
+        n, width = o.shape
+        self._check(self.lib.idm_gate_scale(_p(o), (gate.data_ptr() if gate is not None else None), gate_stride,
+                                            float(scale), _p(out), out.shape[1], out_col, n, width, self._stream()))
 
     def attention_tc_plan(self, ctx, n_q: int, n_kv: int, hd: int, through_scratch=None, share=None):
         """What the attention launches of one step share, for one arrangement of heads: the list of tiles

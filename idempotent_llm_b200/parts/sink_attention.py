@@ -90,7 +90,12 @@ class SinkAttention(Mixer):
         if s.conv_taps > 1 and not ctx.single_token:
             K.conv_state_update(proj, col0, self.channels, s.conv_taps, state, ctx)
         gate = proj[:, col0 + self.channels:col0 + self.channels + self.inner] if s.gate else None
-        K.attention_sink(q, kv, ctx, s.softmax_scale, self.sink, gate, proj.shape[1], out, out_col, out_scale)
+        if K.attention_tc_fits(kv, s.key_dim, s.value_dim):
+            # on the tensor cores, for prompts and single tokens alike; gate and constant in a pass of their own
+            o = K.attention_tc(q, kv, ctx, s.softmax_scale, sink=self.sink)
+            K.gate_scale(o, gate, proj.shape[1], out_scale, out, out_col)
+        else:
+            K.attention_sink(q, kv, ctx, s.softmax_scale, self.sink, gate, proj.shape[1], out, out_col, out_scale)
 
     def forward(self, x, ctx, kv, state, writes_cache: bool):
         if not writes_cache:

@@ -136,9 +136,15 @@ def _plain_left(x, w, s):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("variant", ["all", "bare", "whole_head", "wide_keys"])
+@pytest.mark.parametrize("variant", ["all", "bare", "whole_head", "wide_keys", "tensor_core_64", "tensor_core_128"])
 def test_sink_attention_alone_prompt_then_single_tokens(dtype, variant):
+    """(Key and value rows of 64 or 128 elements take the tensor-core attention in bfloat16, which folds the sink
+    behind the last run of keys; every other shape, and 32-bit, the general kernel.)"""
     spec = {"all": _sink_spec(),
+            "tensor_core_64": _sink_spec(key_dim=64, value_dim=64, n_heads=4, n_kv_heads=2, softmax_scale=0.15,
+                                         position=RotarySpec(3e4, 32, 1 << 20, variant="half_partial")),
+            "tensor_core_128": _sink_spec(key_dim=128, value_dim=128, n_heads=3, n_kv_heads=1, softmax_scale=0.1, gate=False,
+                                          position=RotarySpec(3e4, 128, 1 << 20, variant="half_partial")),
             "bare": _sink_spec(conv_taps=1, position=None, sink=False, gate=False, n_kv_heads=6),
             "whole_head": _sink_spec(position=RotarySpec(1e4, 24, 1 << 20, variant="half_partial"), conv_taps=2, n_kv_heads=1),
             "wide_keys": _sink_spec(key_dim=72, value_dim=8, n_heads=2, n_kv_heads=1,
