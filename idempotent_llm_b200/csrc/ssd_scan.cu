@@ -21,6 +21,7 @@
 #define SSD_NS 4            // threads per column of the state
 #define SSD_PB 16           // columns of the state per block
 #define SSD_CHUNK 16        // tokens staged in shared memory at a time
+#define SSD_LCH 128         // tokens of a chunk when long portions are cut to run side by side
 
 struct SsdArgs {
     const float* xbc; int xbc_stride; int x_col, b_col, c_col;    // filtered projection
@@ -30,64 +31,122 @@ struct SsdArgs {
     float* y; int y_stride;                                        // [N_tok, heads * P] gated output
     const int* cu_q; const int* slots;
     int heads, groups, P, N;
+    // long portions in chunks (see the kernel): the chunks' borders in packed tokens, each sequence's first chunk,
+    // scratch for the chunks' states [n_chunks, heads, N, P] and the decays' running products [N_tok, heads]
+    const int* chunk_t0; const int* seq_chunk0;
+    float* chunk_state; float* cum;
 };
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-template <int NPT>
+// MODE 0: a sequence's tokens of this step in order, from and to its state (single tokens, short portions).
+// Long portions are cut into chunks of SSD_LCH tokens that run side by side:
+// MODE 1: a chunk from a zero state: y_raw = (its own tokens' part of S)^T C + D x, not yet gated; the chunk's end
+//         state to scratch; per token the product of the decays from the chunk's start (cum);
+// (ssd_chunk_carry_kernel: chunk after chunk, S_in[c+1] = cum_end[c] S_in[c] + S_end[c], from and to the state)
+// MODE 2: y = (y_raw + cum_t * S_in^T C_t) * silu(z): what the state before the chunk adds, then the gate.
+// The sum over a token's past is the same sum, cut at the chunks' borders: equal up to rounding.
+template <int NPT, int MODE>
 __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    const int s = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SSD_PB;
+    const int h = blockIdx.y, p0 = blockIdx.z * SSD_PB;
     const int g = h / (a.heads / a.groups);
     const int pl = threadIdx.x / SSD_NS, ns = threadIdx.x % SSD_NS;
     const int p = p0 + pl;
     const bool live = p < a.P;
-    const int t0 = a.cu_q[s], t1 = a.cu_q[s + 1];
+    int t0, t1;
+    float* st;
+    if (MODE == 0) {
+        const int s = blockIdx.x;
+        t0 = a.cu_q[s]; t1 = a.cu_q[s + 1];
+        st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * a.N * a.P;
+    } else {
+        t0 = a.chunk_t0[blockIdx.x]; t1 = a.chunk_t0[blockIdx.x + 1];
+        st = a.chunk_state + ((size_t)blockIdx.x * a.heads + h) * a.N * a.P;
+    }
     constexpr int ROW = NPT + 4;                 // a quarter of N, padded: the quarters' rows start 4 banks apart
-    float* sB = sm;                              // [CHUNK][4][ROW]
+    float* sB = sm;                              // [CHUNK][4][ROW]   (MODE 2 stages C only)
     float* sC = sB + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][4][ROW]
     float* sX = sC + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][PB]
     float* sZ = sX + SSD_CHUNK * SSD_PB;         // [CHUNK][PB]
     float* sDt = sZ + SSD_CHUNK * SSD_PB;        // [CHUNK] step sizes, [CHUNK] decays
-    float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * a.N * a.P;
     float S[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = ns * NPT + i;
-        S[i] = (live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
+        S[i] = (MODE != 1 && live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
     }
     const float neg_a = -expf(a.a_log[h]), dskip = a.d_skip[h], bias = a.dt_bias[h];
+    float cum = 1.f;                             // MODE 1: product of the decays since the chunk's start
     for (int tc = t0; tc < t1; tc += SSD_CHUNK) {
         const int nt = min(SSD_CHUNK, t1 - tc);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * SSD_NS * NPT; i += blockDim.x) {
-            const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
-            const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride;
-            const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
-            sB[at] = n < a.N ? row[a.b_col + g * a.N + n] : 0.f;          // (zeros past N: those state elements stay zero)
-            sC[at] = n < a.N ? row[a.c_col + g * a.N + n] : 0.f;
+        // B and C of the chunk's tokens: eight loads of a thread in flight at a time
+        const int total = nt * SSD_NS * NPT;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
+            float vb[8], vc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * SSD_NS * SSD_PB;
+                const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
+                const bool in = i < total && n < a.N;
+                const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
+                vb[u] = (MODE != 2 && in) ? row[a.b_col] : 0.f;          // (zeros past N: those state elements stay zero)
+                vc[u] = in ? row[a.c_col] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * SSD_NS * SSD_PB;
+                if (i < total) {
+                    const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
+                    const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
+                    if (MODE != 2) sB[at] = vb[u];
+                    sC[at] = vc[u];
+                }
+            }
         }
         for (int i = threadIdx.x; i < nt * SSD_PB; i += blockDim.x) {
             const int tt = i / SSD_PB, pp = p0 + i % SSD_PB;
             const bool in = pp < a.P;
-            sX[i] = in ? a.xbc[(size_t)(tc + tt) * a.xbc_stride + a.x_col + h * a.P + pp] : 0.f;
-            sZ[i] = in ? a.proj[(size_t)(tc + tt) * a.proj_stride + a.z_col + h * a.P + pp] : 0.f;
+            if (MODE != 2) sX[i] = in ? a.xbc[(size_t)(tc + tt) * a.xbc_stride + a.x_col + h * a.P + pp] : 0.f;
+            else sX[i] = in ? a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + pp] : 0.f;          // y_raw
+            if (MODE != 1) sZ[i] = in ? a.proj[(size_t)(tc + tt) * a.proj_stride + a.z_col + h * a.P + pp] : 0.f;
         }
         if (threadIdx.x < nt) {
-            const float dt = softplus_f(a.proj[(size_t)(tc + threadIdx.x) * a.proj_stride + a.dt_col + h] + bias);
-            sDt[threadIdx.x] = dt;
-            sDt[SSD_CHUNK + threadIdx.x] = expf(neg_a * dt);
+            if (MODE == 2) {
+                sDt[threadIdx.x] = a.cum[(size_t)(tc + threadIdx.x) * a.heads + h];
+            } else {
+                const float dt = softplus_f(a.proj[(size_t)(tc + threadIdx.x) * a.proj_stride + a.dt_col + h] + bias);
+                sDt[threadIdx.x] = dt;
+                sDt[SSD_CHUNK + threadIdx.x] = expf(neg_a * dt);
+            }
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
+            const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
+            float acc = 0.f;
+            if (MODE == 2) {
+#pragma unroll
+                for (int i = 0; i < NPT / 4; ++i) {
+                    const float4 c = Ct[i];
+                    acc = fmaf(S[4 * i], c.x, acc); acc = fmaf(S[4 * i + 1], c.y, acc);
+                    acc = fmaf(S[4 * i + 2], c.z, acc); acc = fmaf(S[4 * i + 3], c.w, acc);
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                if (ns == 0 && live) {
+                    const float z = sZ[tt * SSD_PB + pl];
+                    const float yv = fmaf(sDt[tt], acc, sX[tt * SSD_PB + pl]);
+                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
+                }
+                continue;
+            }
             const float dt = sDt[tt], decay = sDt[SSD_CHUNK + tt];
             const float x = sX[tt * SSD_PB + pl];
             const float dtx = dt * x;
             const float4* Bt = reinterpret_cast<const float4*>(sB + (tt * SSD_NS + ns) * ROW);
-            const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
-            float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < NPT / 4; ++i) {
                 const float4 b = Bt[i], c = Ct[i];
@@ -98,13 +157,22 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (MODE == 1) {
+                cum *= decay;
+                if (threadIdx.x == 0 && blockIdx.z == 0) a.cum[(size_t)(tc + tt) * a.heads + h] = cum;
+            }
             if (ns == 0 && live) {
-                const float z = sZ[tt * SSD_PB + pl];
                 const float yv = fmaf(dskip, x, acc);
-                a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
+                if (MODE == 1) {
+                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv;
+                } else {
+                    const float z = sZ[tt * SSD_PB + pl];
+                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
+                }
             }
         }
     }
+    if (MODE == 2) return;
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = ns * NPT + i;
@@ -112,32 +180,74 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     }
 }
 
+// Between the two passes over the chunks: for every sequence, head and state element, chunk after chunk:
+// what the chunk starts from takes the place of the chunk's own end state in scratch, and the state moves on:
+// S <- cum_end[c] * S + S_end[c].  From the sequence's state, and back to it.
+__global__ void __launch_bounds__(256) ssd_chunk_carry_kernel(SsdArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int c0 = a.seq_chunk0[s], c1 = a.seq_chunk0[s + 1];
+    const size_t per = (size_t)a.N * a.P;
+    float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * per;
+    for (size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x; e < per; e += (size_t)gridDim.z * blockDim.x) {
+        float S = st[e];
+        for (int c = c0; c < c1; ++c) {
+            float* cs = a.chunk_state + ((size_t)c * a.heads + h) * per + e;
+            const float end = *cs;
+            *cs = S;
+            S = fmaf(a.cum[(size_t)(a.chunk_t0[c + 1] - 1) * a.heads + h], S, end);
+        }
+        st[e] = S;
+    }
+}
+
+template <int MODE>
+static int ssd_launch(const SsdArgs& a, dim3 grid, cudaStream_t stream) {
+    const dim3 block(SSD_NS * SSD_PB);
+    const int npt = (a.N + SSD_NS - 1) / SSD_NS;
+    const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
+    const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
+    if (npt <= 8) idm_launch(ssd_scan_kernel<8, MODE>, grid, block, smem, stream, a);
+    else if (npt <= 16) idm_launch(ssd_scan_kernel<16, MODE>, grid, block, smem, stream, a);
+    else if (npt <= 32) idm_launch(ssd_scan_kernel<32, MODE>, grid, block, smem, stream, a);
+    else idm_launch(ssd_scan_kernel<64, MODE>, grid, block, smem, stream, a);
+    IDM_LAUNCH_CHECK("ssd_scan");
+    return 0;
+}
+
+extern "C" int idm_ssd_chunk_tokens() { return SSD_LCH; }
+
+// chunk_t0 [n_chunks + 1]: the chunks' first packed tokens (a chunk ends where the next begins; chunks never
+// cross a sequence's border); seq_chunk0 [n_seqs + 1]: each sequence's first chunk; n_chunks == 0: every sequence
+// token by token from its state.  scratch: n_chunks * heads * N * P floats, then n_tokens * heads.
 extern "C" int idm_ssd_scan(const float* xbc, int xbc_stride, int x_col, int b_col, int c_col, const float* proj,
                             int proj_stride, int z_col, int dt_col, const float* dt_bias, const float* a_log,
                             const float* d_skip, float* state, long long state_stride, float* y, int y_stride,
                             const int* cu_q, const int* slots, int n_seqs, int heads, int groups, int P, int N,
+                            const int* chunk_t0, const int* seq_chunk0, int n_chunks, float* scratch, int n_tokens,
                             cudaStream_t stream) {
     if (n_seqs == 0) return 0;
     IDM_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && P > 0 && N > 0 && N <= 256,
                 "ssd_scan: %d heads in %d groups, columns %d, state %d (at most 256)", heads, groups, P, N);
     IDM_REQUIRE(state_stride >= (long long)heads * N * P, "ssd_scan: a slot's state must hold %d x %d x %d floats", heads, N, P);
     IDM_REQUIRE(n_seqs <= 65535 && heads <= 65535, "ssd_scan: %d sequences, %d heads in one launch", n_seqs, heads);
+    IDM_REQUIRE(n_chunks == 0 || (chunk_t0 && seq_chunk0 && scratch), "ssd_scan: chunks need their lists and scratch");
     SsdArgs a;
     a.xbc = xbc; a.xbc_stride = xbc_stride; a.x_col = x_col; a.b_col = b_col; a.c_col = c_col;
     a.proj = proj; a.proj_stride = proj_stride; a.z_col = z_col; a.dt_col = dt_col;
     a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.state = state; a.state_stride = state_stride;
     a.y = y; a.y_stride = y_stride; a.cu_q = cu_q; a.slots = slots;
     a.heads = heads; a.groups = groups; a.P = P; a.N = N;
-    const dim3 grid(n_seqs, heads, (P + SSD_PB - 1) / SSD_PB), block(SSD_NS * SSD_PB);
-    const int npt = (N + SSD_NS - 1) / SSD_NS;
-    const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
-    const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
-    if (npt <= 8) idm_launch(ssd_scan_kernel<8>, grid, block, smem, stream, a);
-    else if (npt <= 16) idm_launch(ssd_scan_kernel<16>, grid, block, smem, stream, a);
-    else if (npt <= 32) idm_launch(ssd_scan_kernel<32>, grid, block, smem, stream, a);
-    else idm_launch(ssd_scan_kernel<64>, grid, block, smem, stream, a);
-    IDM_LAUNCH_CHECK("ssd_scan");
-    return 0;
+    a.chunk_t0 = chunk_t0; a.seq_chunk0 = seq_chunk0; a.chunk_state = scratch;
+    a.cum = scratch ? scratch + (size_t)n_chunks * heads * N * P : nullptr;
+    const int pz = (P + SSD_PB - 1) / SSD_PB;
+    if (n_chunks == 0) return ssd_launch<0>(a, dim3(n_seqs, heads, pz), stream);
+    if (ssd_launch<1>(a, dim3(n_chunks, heads, pz), stream)) return 1;
+    const int ez = (int)(((size_t)N * P + 1023) / 1024);
+    idm_launch(ssd_chunk_carry_kernel, dim3(n_seqs, heads, ez < 1 ? 1 : ez), dim3(256), 0, stream, a);
+    IDM_LAUNCH_CHECK("ssd_chunk_carry");
+    return ssd_launch<2>(a, dim3(n_chunks, heads, pz), stream);
 }
 
 // out[t, out_col + c] = y[t, c] / sqrt(mean over c's part of y^2 + eps) * w[c] * scale.  One warp per (token, part).

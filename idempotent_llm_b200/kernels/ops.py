@@ -65,7 +65,8 @@ SIGNATURES = {
     "idm_short_conv": (c_int, "piiiippipqppppppip"),
     "idm_conv_qkv_cache": (c_int, "piiippqiiiiipppppipppppip"),
     "idm_conv_state_update": (c_int, "piiiipqppppip"),
-    "idm_ssd_scan": (c_int, "piiiipiiippppqpippiiiiip"),
+    "idm_ssd_chunk_tokens": (c_int, ""),
+    "idm_ssd_scan": (c_int, "piiiipiiippppqpippiiiiippipip"),
     "idm_ssd_group_norm": (c_int, "piipffpiiip"),
     "idm_attention_sink": (c_int, "ppiifpppippipppppiiiiifip"),
     "idm_gemm_bf16_gated": (c_int, "pppiiiip"),
@@ -299,18 +300,45 @@ class Kernels:
                                                    self._state_stride(state), _p(ctx.slots), _p(ctx.q_start),
                                                    _p(ctx.cu_q), _p(ctx.kv_len), ctx.n_seqs, self._stream()))
 
+    def ssd_chunks(self, ctx):
+        """How a step's long portions are cut for the state-space recurrence: (chunk borders in packed tokens
+        [n_chunks + 1], each sequence's first chunk [n_seqs + 1], n_chunks), on the device, made once a step; None
+        when no sequence brings more than a chunk's tokens (then every sequence runs token by token from its state)."""
+        L = self.lib.idm_ssd_chunk_tokens()
+        if ctx.single_token or ctx.max_q_len <= L:
+            return None
+        plan = ctx.memo.get("ssd_chunks")
+        if plan is None:
+            borders, first, at = [], [0], 0
+            for n in ctx.host_q_lens:
+                borders += list(range(at, at + n, L))
+                at += n
+                first.append(len(borders))
+            borders.append(at)
+            dev = torch.tensor(borders + first, dtype=torch.int32).to(self.device)
+            plan = ctx.memo["ssd_chunks"] = (dev, dev[:len(borders)], dev[len(borders):], len(borders) - 1)
+        return plan
+
     def ssd_scan(self, xbc, cols, proj, z_col: int, dt_col: int, dt_bias, a_log, d_skip, state, ctx, heads, groups,
                  P, N) -> torch.Tensor:
         """The state-space recurrence over the step's tokens, sequence by sequence; returns the gated output
-        ``y * silu(z)`` in 32-bit ``[N_tok, heads * P]`` and moves ``state [slots, heads * N * P]`` on."""
+        ``y * silu(z)`` in 32-bit ``[N_tok, heads * P]`` and moves ``state [slots, heads * N * P]`` on.  Steps with
+        long portions run them in chunks side by side (``ssd_chunks``)."""
         self._need(xbc, torch.float32, "filtered projection")
         self._need(proj, torch.float32, "projection")
         n = xbc.shape[0]
         y = torch.empty((n, heads * P), dtype=torch.float32, device=self.device)
+        plan = self.ssd_chunks(ctx)
+        chunk_t0 = seq_chunk0 = scratch = None
+        n_chunks = 0
+        if plan is not None:
+            _, chunk_t0, seq_chunk0, n_chunks = plan
+            scratch = self.scratch("ssd_scan", n_chunks * heads * N * P + n * heads)
         self._check(self.lib.idm_ssd_scan(_p(xbc), xbc.shape[1], cols[0], cols[1], cols[2], _p(proj), proj.shape[1],
                                           z_col, dt_col, _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
                                           self._state_stride(state), _p(y), heads * P, _p(ctx.cu_q), _p(ctx.slots),
-                                          ctx.n_seqs, heads, groups, P, N, self._stream()))
+                                          ctx.n_seqs, heads, groups, P, N, _p(chunk_t0), _p(seq_chunk0), n_chunks,
+                                          _p(scratch), n, self._stream()), 3 if n_chunks else 1)
         return y
 
     def ssd_group_norm(self, y, parts: int, w, eps: float, scale: float, out, out_col: int) -> None:

@@ -218,11 +218,11 @@ def test_state_space_mixer_alone_in_portions(dtype, variant):
     cache = SequenceCache({0: cls.cache_need(spec)}, 64 * 4, DT[dtype], "cuda:0", max_seqs=3)
     cache.alloc_slot()
     slot = cache.alloc_slot()
-    T = 90
+    T = 700                                   # (portions of more than 128 tokens run in chunks side by side)
     x = (torch.randn(T, spec.hidden, generator=torch.Generator().manual_seed(4)) * 1.2).to(DT[dtype])
     ref = plain.right_mixer(x.double(), _w64(w), "R.", _plain_right_cfg(spec), spec.norm_eps)
     outs = []
-    for lo, hi in _cuts(T, [1, 2, 1, 7, 40, 1, 1, 2]):
+    for lo, hi in _cuts(T, [1, 2, 1, 7, 40, 1, 129, 1, 300, 2, 128, 1]):
         ctx = _ctx([slot], [lo], [hi - lo])
         outs.append(part.forward(x[lo:hi].contiguous().cuda(), ctx, None, cache.state_of(0), True).sum(0))
     assert helpers.rel_err(torch.cat(outs), ref) < TOL[dtype]
