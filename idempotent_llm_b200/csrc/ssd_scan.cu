@@ -46,7 +46,7 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // (ssd_chunk_carry_kernel: chunk after chunk, S_in[c+1] = cum_end[c] S_in[c] + S_end[c], from and to the state)
 // MODE 2: y = (y_raw + cum_t * S_in^T C_t) * silu(z): what the state before the chunk adds, then the gate.
 // The sum over a token's past is the same sum, cut at the chunks' borders: equal up to rounding.
-template <int NPT, int MODE>
+template <int NPT, int MODE, bool VEC>
 __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -84,26 +84,54 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
         const int nt = min(SSD_CHUNK, t1 - tc);
         __syncthreads();
         // B and C of the chunk's tokens: eight loads of a thread in flight at a time
-        const int total = nt * SSD_NS * NPT;
-        for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
-            float vb[8], vc[8];
+        if (VEC) {
+            // 16-byte loads: i counts pieces of four state elements, NPT pieces per token (zeros past N)
+            const int total = nt * NPT;
+            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
+                float4 vb[8], vc[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int i = i0 + u * SSD_NS * SSD_PB;
-                const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
-                const bool in = i < total && n < a.N;
-                const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
-                vb[u] = (MODE != 2 && in) ? row[a.b_col] : 0.f;          // (zeros past N: those state elements stay zero)
-                vc[u] = in ? row[a.c_col] : 0.f;
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * SSD_NS * SSD_PB;
+                    const int tt = i / NPT, n = (i % NPT) * 4;
+                    const bool in = i < total && n < a.N;
+                    const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
+                    vb[u] = vc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (MODE != 2 && in) vb[u] = *reinterpret_cast<const float4*>(row + a.b_col);
+                    if (in) vc[u] = *reinterpret_cast<const float4*>(row + a.c_col);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * SSD_NS * SSD_PB;
+                    if (i < total) {
+                        const int tt = i / NPT, n = (i % NPT) * 4;
+                        const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
+                        if (MODE != 2) *reinterpret_cast<float4*>(sB + at) = vb[u];
+                        *reinterpret_cast<float4*>(sC + at) = vc[u];
+                    }
+                }
             }
+        } else {
+            const int total = nt * SSD_NS * NPT;
+            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
+                float vb[8], vc[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int i = i0 + u * SSD_NS * SSD_PB;
-                if (i < total) {
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * SSD_NS * SSD_PB;
                     const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
-                    const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
-                    if (MODE != 2) sB[at] = vb[u];
-                    sC[at] = vc[u];
+                    const bool in = i < total && n < a.N;
+                    const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
+                    vb[u] = (MODE != 2 && in) ? row[a.b_col] : 0.f;          // (zeros past N: those state elements stay zero)
+                    vc[u] = in ? row[a.c_col] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * SSD_NS * SSD_PB;
+                    if (i < total) {
+                        const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
+                        const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
+                        if (MODE != 2) sB[at] = vb[u];
+                        sC[at] = vc[u];
+                    }
                 }
             }
         }
@@ -126,14 +154,17 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
-            float acc = 0.f;
+            // four partial sums side by side (one per element of a 16-byte piece), then (0 + 1) + (2 + 3): the
+            // same order in every mode
+            float ax = 0.f, ay = 0.f, az = 0.f, aw = 0.f, acc;
             if (MODE == 2) {
 #pragma unroll
                 for (int i = 0; i < NPT / 4; ++i) {
                     const float4 c = Ct[i];
-                    acc = fmaf(S[4 * i], c.x, acc); acc = fmaf(S[4 * i + 1], c.y, acc);
-                    acc = fmaf(S[4 * i + 2], c.z, acc); acc = fmaf(S[4 * i + 3], c.w, acc);
+                    ax = fmaf(S[4 * i], c.x, ax); ay = fmaf(S[4 * i + 1], c.y, ay);
+                    az = fmaf(S[4 * i + 2], c.z, az); aw = fmaf(S[4 * i + 3], c.w, aw);
                 }
+                acc = (ax + ay) + (az + aw);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 if (ns == 0 && live) {
@@ -150,11 +181,12 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
 #pragma unroll
             for (int i = 0; i < NPT / 4; ++i) {
                 const float4 b = Bt[i], c = Ct[i];
-                S[4 * i] = fmaf(decay, S[4 * i], dtx * b.x);         acc = fmaf(S[4 * i], c.x, acc);
-                S[4 * i + 1] = fmaf(decay, S[4 * i + 1], dtx * b.y); acc = fmaf(S[4 * i + 1], c.y, acc);
-                S[4 * i + 2] = fmaf(decay, S[4 * i + 2], dtx * b.z); acc = fmaf(S[4 * i + 2], c.z, acc);
-                S[4 * i + 3] = fmaf(decay, S[4 * i + 3], dtx * b.w); acc = fmaf(S[4 * i + 3], c.w, acc);
+                S[4 * i] = fmaf(decay, S[4 * i], dtx * b.x);         ax = fmaf(S[4 * i], c.x, ax);
+                S[4 * i + 1] = fmaf(decay, S[4 * i + 1], dtx * b.y); ay = fmaf(S[4 * i + 1], c.y, ay);
+                S[4 * i + 2] = fmaf(decay, S[4 * i + 2], dtx * b.z); az = fmaf(S[4 * i + 2], c.z, az);
+                S[4 * i + 3] = fmaf(decay, S[4 * i + 3], dtx * b.w); aw = fmaf(S[4 * i + 3], c.w, aw);
             }
+            acc = (ax + ay) + (az + aw);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (MODE == 1) {
@@ -208,10 +240,15 @@ static int ssd_launch(const SsdArgs& a, dim3 grid, cudaStream_t stream) {
     const int npt = (a.N + SSD_NS - 1) / SSD_NS;
     const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
     const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
-    if (npt <= 8) idm_launch(ssd_scan_kernel<8, MODE>, grid, block, smem, stream, a);
-    else if (npt <= 16) idm_launch(ssd_scan_kernel<16, MODE>, grid, block, smem, stream, a);
-    else if (npt <= 32) idm_launch(ssd_scan_kernel<32, MODE>, grid, block, smem, stream, a);
-    else idm_launch(ssd_scan_kernel<64, MODE>, grid, block, smem, stream, a);
+    // B and C in 16-byte loads where every row's pieces lie on 16-byte borders
+    const bool vec = a.N % 4 == 0 && a.xbc_stride % 4 == 0 && a.b_col % 4 == 0 && a.c_col % 4 == 0 && ((uintptr_t)a.xbc & 15) == 0;
+#define SSD_GO(NPT_) (vec ? idm_launch(ssd_scan_kernel<NPT_, MODE, true>, grid, block, smem, stream, a) \
+                          : idm_launch(ssd_scan_kernel<NPT_, MODE, false>, grid, block, smem, stream, a))
+    if (npt <= 8) SSD_GO(8);
+    else if (npt <= 16) SSD_GO(16);
+    else if (npt <= 32) SSD_GO(32);
+    else SSD_GO(64);
+#undef SSD_GO
     IDM_LAUNCH_CHECK("ssd_scan");
     return 0;
 }
