@@ -19,7 +19,7 @@
 #include "common.cuh"
 
 #define SSD_NS 4            // threads per column of the state
-#define SSD_PB 16           // columns of the state per block
+#define SSD_PB 32           // columns of the state per block
 #define SSD_CHUNK 16        // tokens staged in shared memory at a time
 #define SSD_LCH 128         // tokens of a chunk when long portions are cut to run side by side
 
@@ -72,11 +72,14 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
     float* sX = sC + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][PB]
     float* sZ = sX + SSD_CHUNK * SSD_PB;         // [CHUNK][PB]
     float* sDt = sZ + SSD_CHUNK * SSD_PB;        // [CHUNK] step sizes, [CHUNK] decays
-    float S[NPT];
+    float* sCum = sDt + 2 * SSD_CHUNK;           // [CHUNK] MODE 1: the decays' running product
+    float* sY = sCum + SSD_CHUNK;                // [CHUNK][PB] a token's S^T C per column
+    float2 S[NPT / 2];                           // state elements n = ns * NPT + 2 i, + 1 of column p
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int n = ns * NPT + i;
-        S[i] = (MODE != 1 && live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
+    for (int i = 0; i < NPT / 2; ++i) {
+        const int n = ns * NPT + 2 * i;
+        S[i].x = (MODE != 1 && live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
+        S[i].y = (MODE != 1 && live && n + 1 < a.N) ? st[(size_t)(n + 1) * a.P + p] : 0.f;
     }
     const float neg_a = -expf(a.a_log[h]), dskip = a.d_skip[h], bias = a.dt_bias[h];
     float cum = 1.f;                             // MODE 1: product of the decays since the chunk's start
@@ -152,86 +155,97 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
             }
         }
         __syncthreads();
+        // the tokens in order: two state elements per instruction (fma.f32x2: each half rounds like a single fma),
+        // a token's sum over N in four chains, (0 + 1) + (2 + 3), then over the four threads of the column
         for (int tt = 0; tt < nt; ++tt) {
             const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
-            // four partial sums side by side (one per element of a 16-byte piece), then (0 + 1) + (2 + 3): the
-            // same order in every mode
-            float ax = 0.f, ay = 0.f, az = 0.f, aw = 0.f, acc;
+            float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
             if (MODE == 2) {
 #pragma unroll
                 for (int i = 0; i < NPT / 4; ++i) {
                     const float4 c = Ct[i];
-                    ax = fmaf(S[4 * i], c.x, ax); ay = fmaf(S[4 * i + 1], c.y, ay);
-                    az = fmaf(S[4 * i + 2], c.z, az); aw = fmaf(S[4 * i + 3], c.w, aw);
+                    a01 = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), a01);
+                    a23 = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), a23);
                 }
-                acc = (ax + ay) + (az + aw);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                if (ns == 0 && live) {
-                    const float z = sZ[tt * SSD_PB + pl];
-                    const float yv = fmaf(sDt[tt], acc, sX[tt * SSD_PB + pl]);
-                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
-                }
-                continue;
-            }
-            const float dt = sDt[tt], decay = sDt[SSD_CHUNK + tt];
-            const float x = sX[tt * SSD_PB + pl];
-            const float dtx = dt * x;
-            const float4* Bt = reinterpret_cast<const float4*>(sB + (tt * SSD_NS + ns) * ROW);
+            } else {
+                const float decay = sDt[SSD_CHUNK + tt];
+                const float dtx = sDt[tt] * sX[tt * SSD_PB + pl];
+                const float2 decay2 = make_float2(decay, decay), dtx2 = make_float2(dtx, dtx);
+                const float4* Bt = reinterpret_cast<const float4*>(sB + (tt * SSD_NS + ns) * ROW);
 #pragma unroll
-            for (int i = 0; i < NPT / 4; ++i) {
-                const float4 b = Bt[i], c = Ct[i];
-                S[4 * i] = fmaf(decay, S[4 * i], dtx * b.x);         ax = fmaf(S[4 * i], c.x, ax);
-                S[4 * i + 1] = fmaf(decay, S[4 * i + 1], dtx * b.y); ay = fmaf(S[4 * i + 1], c.y, ay);
-                S[4 * i + 2] = fmaf(decay, S[4 * i + 2], dtx * b.z); az = fmaf(S[4 * i + 2], c.z, az);
-                S[4 * i + 3] = fmaf(decay, S[4 * i + 3], dtx * b.w); aw = fmaf(S[4 * i + 3], c.w, aw);
+                for (int i = 0; i < NPT / 4; ++i) {
+                    const float4 b = Bt[i], c = Ct[i];
+                    S[2 * i] = __ffma2_rn(decay2, S[2 * i], __fmul2_rn(dtx2, make_float2(b.x, b.y)));
+                    S[2 * i + 1] = __ffma2_rn(decay2, S[2 * i + 1], __fmul2_rn(dtx2, make_float2(b.z, b.w)));
+                    a01 = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), a01);
+                    a23 = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), a23);
+                }
+                if (MODE == 1) {
+                    cum *= decay;
+                    if (threadIdx.x == 0) sCum[tt] = cum;
+                }
             }
-            acc = (ax + ay) + (az + aw);
+            float acc = (a01.x + a01.y) + (a23.x + a23.y);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (MODE == 1) {
-                cum *= decay;
-                if (threadIdx.x == 0 && blockIdx.z == 0) a.cum[(size_t)(tc + tt) * a.heads + h] = cum;
-            }
-            if (ns == 0 && live) {
-                const float yv = fmaf(dskip, x, acc);
-                if (MODE == 1) {
-                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv;
-                } else {
-                    const float z = sZ[tt * SSD_PB + pl];
-                    a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + p] = yv * (z / (1.0f + expf(-z)));
-                }
-            }
+            if (ns == 0) sY[tt * SSD_PB + pl] = acc;
         }
+        __syncthreads();
+        // what goes out for the chunk's tokens, every thread a few (token, column) pairs
+        for (int i = threadIdx.x; i < nt * SSD_PB; i += blockDim.x) {
+            const int tt = i / SSD_PB, pp = p0 + i % SSD_PB;
+            if (pp >= a.P) continue;
+            float yv;
+            if (MODE == 2) yv = fmaf(sDt[tt], sY[i], sX[i]);          // y_raw + cum_t * (S_in^T C_t)
+            else yv = fmaf(dskip, sX[i], sY[i]);
+            if (MODE != 1) { const float z = sZ[i]; yv *= z / (1.0f + expf(-z)); }
+            a.y[(size_t)(tc + tt) * a.y_stride + h * a.P + pp] = yv;
+        }
+        if (MODE == 1 && blockIdx.z == 0 && threadIdx.x < nt) a.cum[(size_t)(tc + threadIdx.x) * a.heads + h] = sCum[threadIdx.x];
     }
     if (MODE == 2) return;
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int n = ns * NPT + i;
-        if (live && n < a.N) st[(size_t)n * a.P + p] = S[i];
+    for (int i = 0; i < NPT / 2; ++i) {
+        const int n = ns * NPT + 2 * i;
+        if (live && n < a.N) st[(size_t)n * a.P + p] = S[i].x;
+        if (live && n + 1 < a.N) st[(size_t)(n + 1) * a.P + p] = S[i].y;
     }
 }
 
 // Between the two passes over the chunks: for every sequence, head and state element, chunk after chunk:
 // what the chunk starts from takes the place of the chunk's own end state in scratch, and the state moves on:
 // S <- cum_end[c] * S + S_end[c].  From the sequence's state, and back to it.
+#define SSD_CARRY_BATCH 8
 __global__ void __launch_bounds__(256) ssd_chunk_carry_kernel(SsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float cum_end[SSD_CARRY_BATCH];
     const int s = blockIdx.x, h = blockIdx.y;
     const int c0 = a.seq_chunk0[s], c1 = a.seq_chunk0[s + 1];
     const size_t per = (size_t)a.N * a.P;
-    float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * per;
-    for (size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x; e < per; e += (size_t)gridDim.z * blockDim.x) {
-        float S = st[e];
-        for (int c = c0; c < c1; ++c) {
-            float* cs = a.chunk_state + ((size_t)c * a.heads + h) * per + e;
-            const float end = *cs;
-            *cs = S;
-            S = fmaf(a.cum[(size_t)(a.chunk_t0[c + 1] - 1) * a.heads + h], S, end);
+    const size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
+    const bool live = e < per;
+    float* st = a.state + (size_t)a.slots[s] * a.state_stride + (size_t)h * per + e;
+    float S = live ? *st : 0.f;
+    // a batch of chunks at a time: their loads are in flight together, only the sums are a chain
+    for (int b0 = c0; b0 < c1; b0 += SSD_CARRY_BATCH) {
+        const int nb = min(SSD_CARRY_BATCH, c1 - b0);
+        __syncthreads();
+        if (threadIdx.x < nb) cum_end[threadIdx.x] = a.cum[(size_t)(a.chunk_t0[b0 + threadIdx.x + 1] - 1) * a.heads + h];
+        float end[SSD_CARRY_BATCH];
+        float* cs = a.chunk_state + ((size_t)b0 * a.heads + h) * per + e;
+#pragma unroll
+        for (int u = 0; u < SSD_CARRY_BATCH; ++u) end[u] = (live && u < nb) ? cs[(size_t)u * a.heads * per] : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < SSD_CARRY_BATCH; ++u) {
+            if (u < nb) {
+                if (live) cs[(size_t)u * a.heads * per] = S;
+                S = fmaf(cum_end[u], S, end[u]);
+            }
         }
-        st[e] = S;
     }
+    if (live) *st = S;
 }
 
 template <int MODE>
@@ -239,7 +253,7 @@ static int ssd_launch(const SsdArgs& a, dim3 grid, cudaStream_t stream) {
     const dim3 block(SSD_NS * SSD_PB);
     const int npt = (a.N + SSD_NS - 1) / SSD_NS;
     const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
-    const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 2 * SSD_CHUNK * SSD_PB + 2 * SSD_CHUNK) * sizeof(float);
+    const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 3 * SSD_CHUNK * SSD_PB + 3 * SSD_CHUNK) * sizeof(float);
     // B and C in 16-byte loads where every row's pieces lie on 16-byte borders
     const bool vec = a.N % 4 == 0 && a.xbc_stride % 4 == 0 && a.b_col % 4 == 0 && a.c_col % 4 == 0 && ((uintptr_t)a.xbc & 15) == 0;
 #define SSD_GO(NPT_) (vec ? idm_launch(ssd_scan_kernel<NPT_, MODE, true>, grid, block, smem, stream, a) \
@@ -281,8 +295,7 @@ extern "C" int idm_ssd_scan(const float* xbc, int xbc_stride, int x_col, int b_c
     const int pz = (P + SSD_PB - 1) / SSD_PB;
     if (n_chunks == 0) return ssd_launch<0>(a, dim3(n_seqs, heads, pz), stream);
     if (ssd_launch<1>(a, dim3(n_chunks, heads, pz), stream)) return 1;
-    const int ez = (int)(((size_t)N * P + 1023) / 1024);
-    idm_launch(ssd_chunk_carry_kernel, dim3(n_seqs, heads, ez < 1 ? 1 : ez), dim3(256), 0, stream, a);
+    idm_launch(ssd_chunk_carry_kernel, dim3(n_seqs, heads, (unsigned)(((size_t)N * P + 255) / 256)), dim3(256), 0, stream, a);
     IDM_LAUNCH_CHECK("ssd_chunk_carry");
     return ssd_launch<2>(a, dim3(n_chunks, heads, pz), stream);
 }
