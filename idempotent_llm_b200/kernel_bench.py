@@ -14,6 +14,8 @@ def run(args) -> int:
     from .config.presets import preset
     from .kernels import Kernels
     cfg = preset(args.size)
+    if args.kernel == "ssd_mixer":
+        return ssd_mixer(args, cfg)
     K = Kernels(torch.bfloat16, "cuda:0")
     # which kernel a product of many tokens takes (defaults: what the library chooses by itself)
     K.gemm_choices(pair=None if getattr(args, "pairs", None) is None else bool(args.pairs),
@@ -111,6 +113,37 @@ def run(args) -> int:
         return step_trace(args)
     else:
         raise ValueError(f"unknown kernel {args.kernel!r}")
+    return 0
+
+
+def ssd_mixer(args, cfg) -> int:
+    """The state-space mixer of a preset's first layer alone (input projection, filter, recurrence, norm, output
+    projection) on ``--batch`` prompts of ``--context`` tokens: ``--size lunulix-0.6b``."""
+    from .cache import SequenceCache
+    from .engine.batch import context_from_packed, pack_step_host
+    from .kernels import Kernels
+    from .parts import MIXERS, Runtime
+    from .weights import random_weights
+    spec = next(b.mixer for b in cfg.to_model_spec().layers[0].mixer.branches if b.mixer.kind == "ssd")
+    dev = torch.device("cuda:0")
+    rt = Runtime(device=dev, dtype=torch.bfloat16, kernels=Kernels(torch.bfloat16, dev))
+    cls = MIXERS.get(spec.kind)
+    part = cls(spec, random_weights(cls.declare(spec, "m."), 1, 0.02, dtype=torch.bfloat16, device="cuda"), "m.", rt)
+    B, T = args.batch, args.context
+    cache = SequenceCache({0: cls.cache_need(spec)}, 64 * B, torch.bfloat16, "cuda:0", max_seqs=B)
+    slots = [cache.alloc_slot() for _ in range(B)]
+    x = torch.randn(B * T, spec.hidden, device="cuda").to(torch.bfloat16)
+    packed, n, q_lens = pack_step_host(slots, [0] * B, [[0] * T] * B)
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [0] * B)
+    for i in range(args.reps + 3):
+        ctx.memo.clear()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        part.forward(x, ctx, None, cache.state_of(0), True)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            print(f"ssd mixer, {B} x {T} tokens: {e0.elapsed_time(e1) * 1e3:.1f} us")
     return 0
 
 
