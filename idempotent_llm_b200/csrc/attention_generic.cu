@@ -68,10 +68,14 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
                 krow = a.cache.k + row * a.hd; vrow = a.cache.v + row * a.dv;
             }
             float dot = 0.f;
-            for (int d = 0; d < a.hd; d += Vec16<T>::N) {
-                Vec16<T> kv; kv.load(krow + d);
+            if (a.hd % Vec16<T>::N == 0) {
+                for (int d = 0; d < a.hd; d += Vec16<T>::N) {
+                    Vec16<T> kv; kv.load(krow + d);
 #pragma unroll
-                for (int e = 0; e < Vec16<T>::N; ++e) dot = fmaf(qs[d + e], kv.get(e), dot);
+                    for (int e = 0; e < Vec16<T>::N; ++e) dot = fmaf(qs[d + e], kv.get(e), dot);
+                }
+            } else {                                  // rows that do not start on 16-byte borders: the same sum, element by element
+                for (int d = 0; d < a.hd; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
             }
             sc = dot * a.scale;
         }
@@ -149,9 +153,8 @@ extern "C" int idm_attention_sink(const void* q, void* out, int out_stride, int 
                                   const int* q_start, const int* cu_q, int n_tokens, int n_q, int n_kv,
                                   int hd, int dv, float scale, int window, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
-    IDM_REQUIRE(hd > 0 && hd % Vec16<T>::N == 0 && hd <= IDM_MAX_HEAD_DIM && dv > 0 && dv <= IDM_MAX_HEAD_DIM,
-                "attention: key size %d must be a multiple of %d, key and value sizes (%d) at most %d", hd, Vec16<T>::N, dv,
-                IDM_MAX_HEAD_DIM);
+    IDM_REQUIRE(hd > 0 && hd <= IDM_MAX_HEAD_DIM && dv > 0 && dv <= IDM_MAX_HEAD_DIM,
+                "attention: key and value sizes %d, %d must be at most %d", hd, dv, IDM_MAX_HEAD_DIM);
     IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d q-heads are no multiple of %d kv-heads", n_q, n_kv);
     IDM_REQUIRE(out_col >= 0 && out_col + n_q * dv <= out_stride, "attention: columns %d..%d of rows of %d", out_col,
                 out_col + n_q * dv, out_stride);

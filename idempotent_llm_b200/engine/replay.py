@@ -82,13 +82,17 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time (room for each request's last page is added)")
     ap.add_argument("--hash", action="store_true", help="append a chain hash of the logits to each 'done' line")
     ap.add_argument("--no-graph", action="store_true", help="do not capture single-token steps in CUDA graphs")
     args = ap.parse_args(argv)
 
     from .. import api
-    lm = api.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens, use_graph=not args.no_graph)
+    from ..cache.spec import PAGE_TOKENS
+    # the cache hands out whole pages: every live request may leave most of its last page empty, so the given
+    # count of tokens gets room for that on top (for up to 64 requests at a time)
+    lm = api.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * (PAGE_TOKENS - 1),
+                  max_seq_len=args.max_tokens, use_graph=not args.no_graph)
     rp = Replayer(lm, args.out, chain_hash=args.hash)
     for raw in sys.stdin:
         raw = raw.strip()

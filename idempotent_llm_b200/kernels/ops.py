@@ -133,6 +133,7 @@ class Kernels:
         self.lib = builder.load(_DT[dtype])
         self.launches = 0                     # kernels of this library launched so far
         self._scratch = {}
+        self._padded_weights = {}
         self._single_tiles = {}
         self._device_index = device.index if device.index is not None else 0
         self._retired = []
@@ -660,8 +661,25 @@ class Kernels:
             raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 in bfloat16 (rows on 16-byte borders)")
         return M, N, Kd
 
+    def _padded(self, x, w):
+        """bfloat16 operands whose inner size is no multiple of 8 (rows would not start on 16-byte borders), with zero
+        columns added to both: the product is the same sum.  The padded matrix is made once and kept."""
+        pad = -x.shape[1] % 8
+        if self.dtype != torch.bfloat16 or not pad:
+            return x, w
+        key = (w.data_ptr(), tuple(w.shape))
+        wp = self._padded_weights.get(key)
+        if wp is None:
+            wp = torch.zeros((w.shape[0], w.shape[1] + pad), dtype=w.dtype, device=w.device)
+            wp[:, :w.shape[1]] = w
+            self._padded_weights[key] = wp
+        xp = torch.zeros((x.shape[0], x.shape[1] + pad), dtype=x.dtype, device=x.device)
+        xp[:, :x.shape[1]] = x
+        return xp, wp
+
     def gemm_store(self, x, w) -> torch.Tensor:
         """``x . w^T`` in 32-bit ``[M, N]``."""
+        x, w = self._padded(x, w)
         M, N, Kd = self._gemm_shape(x, w)
         out = torch.empty((M, N), dtype=torch.float32, device=self.device)
         if M:

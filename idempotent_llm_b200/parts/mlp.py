@@ -36,10 +36,10 @@ class GatedMLP(FeedForward):
         gate, up = weights[prefix + nm.gate].to(rt.dtype), weights[prefix + nm.up].to(rt.dtype)
         # with the fused kernels the activation is the epilogue of the gate/up product, which wants
         # gate and up rows interleaved in tiles; otherwise the rows are simply concatenated
-        if rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8):
-            raise ValueError(f"in bfloat16 the widths of a feed-forward must be multiples of 8 (matrix rows start on "
-                             f"16-byte borders); got hidden {spec.hidden}, intermediate {spec.intermediate}")
-        self.fused = bool(getattr(rt.kernels, "fused", False))
+        # the activation as the product's epilogue wants rows on 16-byte borders; other widths take the product with
+        # padded operands and the activation as a kernel of its own
+        aligned = not (rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8))
+        self.fused = bool(getattr(rt.kernels, "fused", False)) and aligned
         if self.fused:
             self.w_gate_up = rt.kernels.tile_gate_up(gate, up)
         else:

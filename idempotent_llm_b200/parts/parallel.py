@@ -72,8 +72,6 @@ class ParallelMixer(Mixer):
         self.in_weight = torch.cat([p.in_weight for p in self.branches], dim=0).contiguous()
         self.out_weight = torch.cat([p.out_weight for p in self.branches], dim=1).contiguous()
         self.inner = sum(p.inner for p in self.branches)
-        if rt.dtype == torch.bfloat16 and self.inner % 8:
-            raise ValueError(f"in bfloat16 the branches' activations ({self.inner} columns) must be a multiple of 8")
         for p in self.branches:                     # the joint matrices are the ones that are read
             p.in_weight = p.out_weight = None
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.branches)

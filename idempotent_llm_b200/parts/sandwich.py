@@ -33,9 +33,6 @@ class TokenSide(Part):
         s = spec
         if s.activation not in ACTIVATIONS:
             raise ValueError(f"activation {s.activation!r} is not built; known: {sorted(ACTIVATIONS)}")
-        if rt.dtype == torch.bfloat16 and (s.hidden % 8 or s.dim % 8):
-            raise ValueError(f"in bfloat16 the widths of a token side input must be multiples of 8; got hidden "
-                             f"{s.hidden}, dim {s.dim}")
         self.spec, self.rt = spec, rt
         self.act = ACTIVATIONS[s.activation]
         self.table = rt.shared_tensor(weights, s.table, rt.dtype)

@@ -58,9 +58,6 @@ class SinkAttention(Mixer):
         s, nm = spec, spec.names
         if s.n_heads % s.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        if rt.dtype == torch.bfloat16 and (s.hidden % 8 or (s.n_heads * s.value_dim) % 8 or s.key_dim % 8):
-            raise ValueError(f"in bfloat16 the widths of an attention layer must be multiples of 8 (rows start on 16-byte "
-                             f"borders); got hidden {s.hidden}, heads x value_dim {s.n_heads * s.value_dim}, key_dim {s.key_dim}")
         self.spec, self.rt = spec, rt
         mats = [weights[prefix + n] for n in (nm.q, nm.k, nm.v)] + ([weights[prefix + nm.gate]] if s.gate else [])
         self.in_weight = torch.cat([m.to(rt.dtype) for m in mats], dim=0).contiguous()

@@ -58,9 +58,6 @@ class SSDMixer(Mixer):
         if s.heads % s.groups or (s.heads * s.head_dim) % s.norm_groups:
             raise ValueError("heads must be a multiple of groups, and heads * head_dim of norm_groups")
         inner, gn, ch = self._sizes(s)
-        if rt.dtype == torch.bfloat16 and (s.hidden % 8 or inner % 8):
-            raise ValueError(f"in bfloat16 the widths of a state-space mixer must be multiples of 8; got hidden "
-                             f"{s.hidden}, heads x head_dim {inner}")
         self.spec, self.rt = spec, rt
         self.inner, self.gn, self.channels = inner, gn, ch
         self.in_weight = weights[prefix + nm.w_in].to(rt.dtype).contiguous()

@@ -136,10 +136,15 @@ LUNULIX = {
     "Q": lambda: lunulix_config([
         lunulix_layer(heads=3, kv_heads=1, dim=8, vdim=8, lconv=0, rot_dims=0, r_heads=3, r_vdim=8, state=16, groups=3,
                       rconv=2, norm_groups=4, ff=24)], vocab=50, width=24, emb_scale=1.0, side_dim=0),
+    # widths that are no multiple of 8 (bfloat16 rows off the 16-byte borders): products with padded operands, keys
+    # read element by element, the feed-forward's activation as a kernel of its own
+    "S": lambda: lunulix_config([
+        lunulix_layer(heads=3, kv_heads=1, dim=12, vdim=10, scale=0.3, rot_dims=6, r_heads=2, r_vdim=6, state=6, groups=1,
+                      rconv=3, norm_groups=3, ff=28)] * 2, vocab=33, width=20, emb_scale=2.0, side_dim=4),
     # head sizes the tensor-core attention has (64), three layers, width 64
-    "R": lambda: lunulix_config([lunulix_layer(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.125, rot_dims=32,
+    "R": lambda: lunulix_config([lunulix_layer(heads=6, kv_heads=2, dim=64, vdim=64, scale=0.11, rot_dims=48,
                                                r_heads=2, r_vdim=32, state=32, groups=1, ff=96)] * 3,
-                                vocab=211, width=64, emb_scale=8.0, side_dim=16),
+                                vocab=211, width=64, emb_scale=8.0, side_dim=24),
 }
 
 

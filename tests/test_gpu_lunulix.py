@@ -231,7 +231,7 @@ def test_state_space_mixer_alone_in_portions(dtype, variant):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_parallel_mixer_is_the_weighted_sum_of_its_branches(dtype):
     left, right = _sink_spec(), _ssd_spec()
-    spec = ParallelMixerSpec(hidden=40, prefix="mix.", branches=(MixerBranch(left, "left.", 0.6), MixerBranch(right, "right.", 1.7)))
+    spec = ParallelMixerSpec(hidden=40, prefix="mix.", branches=(MixerBranch(left, "left.", 0.8), MixerBranch(right, "right.", 1.7)))
     rt = _rt(dtype)
     cls = MIXERS.get(spec.kind)
     w = random_weights(cls.declare(spec, "l0."), 13, 0.25, dtype=DT[dtype], device="cuda")
@@ -243,7 +243,7 @@ def test_parallel_mixer_is_the_weighted_sum_of_its_branches(dtype):
     T = 70
     x = (torch.randn(T, 40, generator=torch.Generator().manual_seed(8)) * 1.2).to(DT[dtype])
     w64 = _w64(w)
-    ref = (0.6 * plain.left_mixer(x.double(), w64, "l0.mix.left.", _plain_left_cfg(left))
+    ref = (0.8 * plain.left_mixer(x.double(), w64, "l0.mix.left.", _plain_left_cfg(left))
            + 1.7 * plain.right_mixer(x.double(), w64, "l0.mix.right.", _plain_right_cfg(right), 1e-5))
     outs = []
     for lo, hi in _cuts(T, [33, 1, 1, 2, 30, 1]):
@@ -317,7 +317,7 @@ def _step_all(lm, slot, tokens, lo, hi):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompt_and_every_layer_against_plain(lunulix_dirs, name, dtype):
     d = lunulix_dirs(name, dtype)
     lm = api.load(d, dtype=dtype, max_tokens=512)
@@ -342,7 +342,7 @@ def test_whole_prompt_and_every_layer_against_plain(lunulix_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "S"])
 def test_token_by_token_from_the_first_token_equals_the_prompt(lunulix_dirs, name, dtype):
     d = lunulix_dirs(name, dtype)
     lm = api.load(d, dtype=dtype, max_tokens=512)
