@@ -115,7 +115,7 @@ class CausalLM:
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, cache.view(e.cache),
                                                       cache.state_of(e.cache), e.writes_cache)
         x = self.final_norm.forward(h, pending, ctx, rows=want_rows)
-        return K.gemm_store(x, self.head)
+        return K.gemm_store(x, self.head, **({"pad": True} if self.spec.hidden % 8 else {}))
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0

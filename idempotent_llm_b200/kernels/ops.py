@@ -645,10 +645,10 @@ class Kernels:
                                         n, inter, tiled, self._stream()))
         return y
 
-    def gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def gemm(self, x: torch.Tensor, w: torch.Tensor, pad: bool = False) -> torch.Tensor:
         """``x [M, K] . w [N, K]^T`` in 32-bit as ``[1, M, N]`` (the leading axis is the one a part's
         delta carries: partial sums that the consumer adds; these kernels never split a sum)."""
-        return self.gemm_store(x, w).unsqueeze(0)
+        return self.gemm_store(x, w, pad=pad).unsqueeze(0)
 
     def _gemm_shape(self, x, w):
         self._need(x, self.dtype, "gemm input")
@@ -677,9 +677,11 @@ class Kernels:
         xp[:, :x.shape[1]] = x
         return xp, wp
 
-    def gemm_store(self, x, w) -> torch.Tensor:
-        """``x . w^T`` in 32-bit ``[M, N]``."""
-        x, w = self._padded(x, w)
+    def gemm_store(self, x, w, pad: bool = False) -> torch.Tensor:
+        """``x . w^T`` in 32-bit ``[M, N]``.  ``pad``: a bfloat16 inner size that is no multiple of 8 is served with
+        zero columns added to both operands instead of being refused."""
+        if pad:
+            x, w = self._padded(x, w)
         M, N, Kd = self._gemm_shape(x, w)
         out = torch.empty((M, N), dtype=torch.float32, device=self.device)
         if M:

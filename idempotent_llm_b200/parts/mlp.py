@@ -40,6 +40,7 @@ class GatedMLP(FeedForward):
         # padded operands and the activation as a kernel of its own
         aligned = not (rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8))
         self.fused = bool(getattr(rt.kernels, "fused", False)) and aligned
+        self.pad = {} if aligned else {"pad": True}
         if self.fused:
             self.w_gate_up = rt.kernels.tile_gate_up(gate, up)
         else:
@@ -66,6 +67,6 @@ class GatedMLP(FeedForward):
                 K.gemm_residual(y, self.w_down, residual)
                 return None
             return K.gemm(y, self.w_down)
-        gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate]
+        gu = K.gemm(x, self.w_gate_up, **self.pad)          # [P, N, 2 * intermediate]
         y = K.swiglu(gu) if self.act == 0 else K.gated_act(gu[0], self.act)      # [N, intermediate]
-        return K.gemm(y, self.w_down)           # [P, N, hidden]
+        return K.gemm(y, self.w_down, **self.pad)           # [P, N, hidden]

@@ -78,11 +78,11 @@ class ParallelMixer(Mixer):
 
     def forward(self, x, ctx, kv, state, writes_cache: bool):
         K = self.rt.kernels
-        proj = K.gemm_store(x, self.in_weight)                       # 32-bit [N, all branches' rows]
+        proj = K.gemm_store(x, self.in_weight, pad=True)                       # 32-bit [N, all branches' rows]
         out = torch.empty((x.shape[0], self.inner), dtype=self.rt.dtype, device=x.device)
         col0 = out_col = 0
         for p, scale, (a, b), rows in zip(self.branches, self.scales, self.state_cols, self._rows):
             p.mix(proj, col0, ctx, kv, state[:, a:b] if b > a else None, out, out_col, scale)
             col0 += rows
             out_col += p.inner
-        return K.gemm(out, self.out_weight)                          # [1, N, hidden]
+        return K.gemm(out, self.out_weight, pad=True)                          # [1, N, hidden]

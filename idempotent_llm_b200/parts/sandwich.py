@@ -43,8 +43,8 @@ class TokenSide(Part):
     def forward(self, x, ctx):
         """x: the stream in the storage dtype ``[N, hidden]``; returns 32-bit ``[N, hidden]``, not yet normed."""
         K, s = self.rt.kernels, self.spec
-        g = K.token_gate(K.gemm_store(x, self.w_gate), ctx.tokens, self.table, s.col0, self.act)
-        return K.gemm_store(g, self.w_proj)
+        g = K.token_gate(K.gemm_store(x, self.w_gate, pad=True), ctx.tokens, self.table, s.col0, self.act)
+        return K.gemm_store(g, self.w_proj, pad=True)
 
 
 @BLOCKS.register("sandwich")

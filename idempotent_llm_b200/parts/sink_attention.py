@@ -98,7 +98,7 @@ class SinkAttention(Mixer):
         if not writes_cache:
             raise ValueError("this mixer writes its own keys and values")
         K = self.rt.kernels
-        proj = K.gemm_store(x, self.in_weight)
+        proj = K.gemm_store(x, self.in_weight, pad=True)
         out = torch.empty((x.shape[0], self.inner), dtype=self.rt.dtype, device=x.device)
         self.mix(proj, 0, ctx, kv, state, out, 0, 1.0)
-        return K.gemm(out, self.out_weight)
+        return K.gemm(out, self.out_weight, pad=True)

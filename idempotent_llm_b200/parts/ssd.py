@@ -83,7 +83,7 @@ class SSDMixer(Mixer):
 
     def forward(self, x, ctx, kv, state, writes_cache: bool):
         K = self.rt.kernels
-        proj = K.gemm_store(x, self.in_weight)
+        proj = K.gemm_store(x, self.in_weight, pad=True)
         out = torch.empty((x.shape[0], self.inner), dtype=self.rt.dtype, device=x.device)
         self.mix(proj, 0, ctx, None, state, out, 0, 1.0)
-        return K.gemm(out, self.out_weight)
+        return K.gemm(out, self.out_weight, pad=True)
