@@ -434,6 +434,8 @@ def design_comparison(args) -> int:
     sizes = [s for s in args.design_sizes.split(",") if s]
     steps = min(args.steps, 32)
     rows = {}
+    sampler = ClockSampler()
+    sampler.start()
     for size in sizes:
         for arch in ("qwen3", args.design):
             cfg = preset(f"{arch}-{size}")
@@ -455,7 +457,7 @@ def design_comparison(args) -> int:
     print(json.dumps({"metric": f"decode and prefill of {args.design} beside qwen3 at equal sizes (bf16, random weights)",
                       "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
                       "data": "synthetic: seeded random weights and uniform-random token ids", "peaks": pk,
-                      "rows": rows}))
+                      "clocks": sampler.stop(), "rows": rows}))
     return 0
 
 

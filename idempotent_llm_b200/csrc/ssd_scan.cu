@@ -7,19 +7,20 @@
 //
 // x [N_tok, heads, P], B and C [N_tok, groups, N] are columns of one 32-bit buffer (the filtered
 // projection), z and the raw step sizes columns of another (the projection itself).  Head h reads group
-// h / (heads / groups).  One block owns (sequence, head, a slice of P) and walks the sequence's tokens of
-// this step in order; a thread keeps N / 4 state elements of one column p in registers, four threads
-// share a column and add their parts of y by shuffles in a fixed order.  B and C of a few tokens are staged in
-// shared memory, each thread's quarter of N in a row of its own, padded so that the four quarters read by a
-// warp in one 16-byte load fall into different banks.  A step of one token and a step
-// of a thousand run the same operations on the same numbers for every token.
+// h / (heads / groups).  One block owns (sequence or chunk, head, 32 columns of S) and walks its tokens in order.
+// Eight threads share two columns: a thread keeps N / 8 state elements of each in registers, so that a value of B
+// or C read from shared memory serves both columns (the kernel is bound by those reads), and the eight add their
+// parts of y by shuffles in a fixed order.  B and C of 16 tokens are staged in shared memory, each thread's part of
+// N in a row of its own, padded so that the eight rows a warp reads in one 16-byte load fall into different
+// banks.  A step of one token and a portion of a hundred run the same operations on the same numbers for every token.
 //
 // ssd_group_norm: the gated output in `parts` equal parts, each divided by its own root mean square,
 // times a weight and a constant, stored in the storage type at a column offset of a wider buffer.
 #include "common.cuh"
 
-#define SSD_NS 4            // threads per column of the state
+#define SSD_NS 8            // threads per column of the state (each holds two columns)
 #define SSD_PB 32           // columns of the state per block
+#define SSD_THREADS (SSD_NS * SSD_PB / 2)
 #define SSD_CHUNK 16        // tokens staged in shared memory at a time
 #define SSD_LCH 128         // tokens of a chunk when long portions are cut to run side by side
 
@@ -47,15 +48,17 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // MODE 2: y = (y_raw + cum_t * S_in^T C_t) * silu(z): what the state before the chunk adds, then the gate.
 // The sum over a token's past is the same sum, cut at the chunks' borders: equal up to rounding.
 template <int NPT, int MODE, bool VEC>
-__global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
+__global__ void __launch_bounds__(SSD_THREADS) ssd_scan_kernel(SsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
     const int h = blockIdx.y, p0 = blockIdx.z * SSD_PB;
     const int g = h / (a.heads / a.groups);
+    // eight threads share two columns of S (pa, pb), each holding NPT of their N elements: a value of B or C that a
+    // thread reads from shared memory serves both columns
     const int pl = threadIdx.x / SSD_NS, ns = threadIdx.x % SSD_NS;
-    const int p = p0 + pl;
-    const bool live = p < a.P;
+    const int pa = p0 + pl, pb = pa + SSD_PB / 2;
+    const bool live_a = pa < a.P, live_b = pb < a.P;
     int t0, t1;
     float* st;
     if (MODE == 0) {
@@ -66,20 +69,24 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
         t0 = a.chunk_t0[blockIdx.x]; t1 = a.chunk_t0[blockIdx.x + 1];
         st = a.chunk_state + ((size_t)blockIdx.x * a.heads + h) * a.N * a.P;
     }
-    constexpr int ROW = NPT + 4;                 // a quarter of N, padded: the quarters' rows start 4 banks apart
-    float* sB = sm;                              // [CHUNK][4][ROW]   (MODE 2 stages C only)
-    float* sC = sB + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][4][ROW]
+    constexpr int ROW = NPT + 4;                 // a thread's part of N, padded: the eight parts' rows fall into different banks
+    constexpr int PADN = SSD_NS * NPT;           // N rounded up to what the eight threads hold
+    float* sB = sm;                              // [CHUNK][8][ROW]   (MODE 2 stages C only)
+    float* sC = sB + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][8][ROW]
     float* sX = sC + SSD_CHUNK * SSD_NS * ROW;   // [CHUNK][PB]
     float* sZ = sX + SSD_CHUNK * SSD_PB;         // [CHUNK][PB]
     float* sDt = sZ + SSD_CHUNK * SSD_PB;        // [CHUNK] step sizes, [CHUNK] decays
     float* sCum = sDt + 2 * SSD_CHUNK;           // [CHUNK] MODE 1: the decays' running product
     float* sY = sCum + SSD_CHUNK;                // [CHUNK][PB] a token's S^T C per column
-    float2 S[NPT / 2];                           // state elements n = ns * NPT + 2 i, + 1 of column p
+    float2 Sa[NPT / 2], Sb[NPT / 2];             // state elements n = ns * NPT + 2 i, + 1 of columns pa and pb
 #pragma unroll
     for (int i = 0; i < NPT / 2; ++i) {
         const int n = ns * NPT + 2 * i;
-        S[i].x = (MODE != 1 && live && n < a.N) ? st[(size_t)n * a.P + p] : 0.f;
-        S[i].y = (MODE != 1 && live && n + 1 < a.N) ? st[(size_t)(n + 1) * a.P + p] : 0.f;
+        const bool n0 = MODE != 1 && n < a.N, n1 = MODE != 1 && n + 1 < a.N;
+        Sa[i].x = (n0 && live_a) ? st[(size_t)n * a.P + pa] : 0.f;
+        Sa[i].y = (n1 && live_a) ? st[(size_t)(n + 1) * a.P + pa] : 0.f;
+        Sb[i].x = (n0 && live_b) ? st[(size_t)n * a.P + pb] : 0.f;
+        Sb[i].y = (n1 && live_b) ? st[(size_t)(n + 1) * a.P + pb] : 0.f;
     }
     const float neg_a = -expf(a.a_log[h]), dskip = a.d_skip[h], bias = a.dt_bias[h];
     float cum = 1.f;                             // MODE 1: product of the decays since the chunk's start
@@ -88,14 +95,14 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
         __syncthreads();
         // B and C of the chunk's tokens: eight loads of a thread in flight at a time
         if (VEC) {
-            // 16-byte loads: i counts pieces of four state elements, NPT pieces per token (zeros past N)
-            const int total = nt * NPT;
-            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
+            // 16-byte loads: i counts pieces of four state elements, PADN / 4 pieces per token (zeros past N)
+            const int total = nt * (PADN / 4);
+            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_THREADS) {
                 float4 vb[8], vc[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + u * SSD_NS * SSD_PB;
-                    const int tt = i / NPT, n = (i % NPT) * 4;
+                    const int i = i0 + u * SSD_THREADS;
+                    const int tt = i / (PADN / 4), n = (i % (PADN / 4)) * 4;
                     const bool in = i < total && n < a.N;
                     const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
                     vb[u] = vc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -104,9 +111,9 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + u * SSD_NS * SSD_PB;
+                    const int i = i0 + u * SSD_THREADS;
                     if (i < total) {
-                        const int tt = i / NPT, n = (i % NPT) * 4;
+                        const int tt = i / (PADN / 4), n = (i % (PADN / 4)) * 4;
                         const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
                         if (MODE != 2) *reinterpret_cast<float4*>(sB + at) = vb[u];
                         *reinterpret_cast<float4*>(sC + at) = vc[u];
@@ -114,13 +121,13 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
                 }
             }
         } else {
-            const int total = nt * SSD_NS * NPT;
-            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_NS * SSD_PB) {
+            const int total = nt * PADN;
+            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * SSD_THREADS) {
                 float vb[8], vc[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + u * SSD_NS * SSD_PB;
-                    const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
+                    const int i = i0 + u * SSD_THREADS;
+                    const int tt = i / PADN, n = i % PADN;
                     const bool in = i < total && n < a.N;
                     const float* row = a.xbc + (size_t)(tc + tt) * a.xbc_stride + g * a.N + n;
                     vb[u] = (MODE != 2 && in) ? row[a.b_col] : 0.f;          // (zeros past N: those state elements stay zero)
@@ -128,9 +135,9 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + u * SSD_NS * SSD_PB;
+                    const int i = i0 + u * SSD_THREADS;
                     if (i < total) {
-                        const int tt = i / (SSD_NS * NPT), n = i % (SSD_NS * NPT);
+                        const int tt = i / PADN, n = i % PADN;
                         const int at = (tt * SSD_NS + n / NPT) * ROW + n % NPT;
                         if (MODE != 2) sB[at] = vb[u];
                         sC[at] = vc[u];
@@ -156,39 +163,47 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
         }
         __syncthreads();
         // the tokens in order: two state elements per instruction (fma.f32x2: each half rounds like a single fma),
-        // a token's sum over N in four chains, (0 + 1) + (2 + 3), then over the four threads of the column
+        // a token's sum over a thread's part of N in four chains, (0 + 1) + (2 + 3), then over the eight threads
         for (int tt = 0; tt < nt; ++tt) {
             const float4* Ct = reinterpret_cast<const float4*>(sC + (tt * SSD_NS + ns) * ROW);
-            float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
+            float2 a01 = make_float2(0.f, 0.f), a23 = a01, b01 = a01, b23 = a01;
             if (MODE == 2) {
 #pragma unroll
                 for (int i = 0; i < NPT / 4; ++i) {
                     const float4 c = Ct[i];
-                    a01 = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), a01);
-                    a23 = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), a23);
+                    const float2 c01 = make_float2(c.x, c.y), c23 = make_float2(c.z, c.w);
+                    a01 = __ffma2_rn(Sa[2 * i], c01, a01); a23 = __ffma2_rn(Sa[2 * i + 1], c23, a23);
+                    b01 = __ffma2_rn(Sb[2 * i], c01, b01); b23 = __ffma2_rn(Sb[2 * i + 1], c23, b23);
                 }
             } else {
-                const float decay = sDt[SSD_CHUNK + tt];
-                const float dtx = sDt[tt] * sX[tt * SSD_PB + pl];
-                const float2 decay2 = make_float2(decay, decay), dtx2 = make_float2(dtx, dtx);
+                const float decay = sDt[SSD_CHUNK + tt], dt = sDt[tt];
+                const float dxa = dt * sX[tt * SSD_PB + pl], dxb = dt * sX[tt * SSD_PB + pl + SSD_PB / 2];
+                const float2 decay2 = make_float2(decay, decay), dxa2 = make_float2(dxa, dxa), dxb2 = make_float2(dxb, dxb);
                 const float4* Bt = reinterpret_cast<const float4*>(sB + (tt * SSD_NS + ns) * ROW);
 #pragma unroll
                 for (int i = 0; i < NPT / 4; ++i) {
                     const float4 b = Bt[i], c = Ct[i];
-                    S[2 * i] = __ffma2_rn(decay2, S[2 * i], __fmul2_rn(dtx2, make_float2(b.x, b.y)));
-                    S[2 * i + 1] = __ffma2_rn(decay2, S[2 * i + 1], __fmul2_rn(dtx2, make_float2(b.z, b.w)));
-                    a01 = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), a01);
-                    a23 = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), a23);
+                    const float2 bq01 = make_float2(b.x, b.y), bq23 = make_float2(b.z, b.w);
+                    const float2 c01 = make_float2(c.x, c.y), c23 = make_float2(c.z, c.w);
+                    Sa[2 * i] = __ffma2_rn(decay2, Sa[2 * i], __fmul2_rn(dxa2, bq01));
+                    Sa[2 * i + 1] = __ffma2_rn(decay2, Sa[2 * i + 1], __fmul2_rn(dxa2, bq23));
+                    Sb[2 * i] = __ffma2_rn(decay2, Sb[2 * i], __fmul2_rn(dxb2, bq01));
+                    Sb[2 * i + 1] = __ffma2_rn(decay2, Sb[2 * i + 1], __fmul2_rn(dxb2, bq23));
+                    a01 = __ffma2_rn(Sa[2 * i], c01, a01); a23 = __ffma2_rn(Sa[2 * i + 1], c23, a23);
+                    b01 = __ffma2_rn(Sb[2 * i], c01, b01); b23 = __ffma2_rn(Sb[2 * i + 1], c23, b23);
                 }
                 if (MODE == 1) {
                     cum *= decay;
                     if (threadIdx.x == 0) sCum[tt] = cum;
                 }
             }
-            float acc = (a01.x + a01.y) + (a23.x + a23.y);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (ns == 0) sY[tt * SSD_PB + pl] = acc;
+            float ya = (a01.x + a01.y) + (a23.x + a23.y), yb = (b01.x + b01.y) + (b23.x + b23.y);
+#pragma unroll
+            for (int o = 1; o < SSD_NS; o <<= 1) {
+                ya += __shfl_xor_sync(0xffffffffu, ya, o);
+                yb += __shfl_xor_sync(0xffffffffu, yb, o);
+            }
+            if (ns == 0) { sY[tt * SSD_PB + pl] = ya; sY[tt * SSD_PB + pl + SSD_PB / 2] = yb; }
         }
         __syncthreads();
         // what goes out for the chunk's tokens, every thread a few (token, column) pairs
@@ -207,8 +222,10 @@ __global__ void __launch_bounds__(SSD_NS * SSD_PB) ssd_scan_kernel(SsdArgs a) {
 #pragma unroll
     for (int i = 0; i < NPT / 2; ++i) {
         const int n = ns * NPT + 2 * i;
-        if (live && n < a.N) st[(size_t)n * a.P + p] = S[i].x;
-        if (live && n + 1 < a.N) st[(size_t)(n + 1) * a.P + p] = S[i].y;
+        if (live_a && n < a.N) st[(size_t)n * a.P + pa] = Sa[i].x;
+        if (live_a && n + 1 < a.N) st[(size_t)(n + 1) * a.P + pa] = Sa[i].y;
+        if (live_b && n < a.N) st[(size_t)n * a.P + pb] = Sb[i].x;
+        if (live_b && n + 1 < a.N) st[(size_t)(n + 1) * a.P + pb] = Sb[i].y;
     }
 }
 
@@ -250,18 +267,18 @@ __global__ void __launch_bounds__(256) ssd_chunk_carry_kernel(SsdArgs a) {
 
 template <int MODE>
 static int ssd_launch(const SsdArgs& a, dim3 grid, cudaStream_t stream) {
-    const dim3 block(SSD_NS * SSD_PB);
+    const dim3 block(SSD_THREADS);
     const int npt = (a.N + SSD_NS - 1) / SSD_NS;
-    const int npt_t = npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
+    const int npt_t = npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : 32;
     const size_t smem = (size_t)(2 * SSD_CHUNK * SSD_NS * (npt_t + 4) + 3 * SSD_CHUNK * SSD_PB + 3 * SSD_CHUNK) * sizeof(float);
     // B and C in 16-byte loads where every row's pieces lie on 16-byte borders
     const bool vec = a.N % 4 == 0 && a.xbc_stride % 4 == 0 && a.b_col % 4 == 0 && a.c_col % 4 == 0 && ((uintptr_t)a.xbc & 15) == 0;
 #define SSD_GO(NPT_) (vec ? idm_launch(ssd_scan_kernel<NPT_, MODE, true>, grid, block, smem, stream, a) \
                           : idm_launch(ssd_scan_kernel<NPT_, MODE, false>, grid, block, smem, stream, a))
-    if (npt <= 8) SSD_GO(8);
+    if (npt <= 4) SSD_GO(4);
+    else if (npt <= 8) SSD_GO(8);
     else if (npt <= 16) SSD_GO(16);
-    else if (npt <= 32) SSD_GO(32);
-    else SSD_GO(64);
+    else SSD_GO(32);
 #undef SSD_GO
     IDM_LAUNCH_CHECK("ssd_scan");
     return 0;
