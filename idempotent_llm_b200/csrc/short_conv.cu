@@ -28,34 +28,46 @@ struct ConvStep {
     const int* token_seq; const int* positions; const int* slots; const int* q_start; const int* cu_q;
 };
 
-// the convolution of token t, channel c; moves the state on if t is its sequence's only token
-__device__ __forceinline__ float conv_at(const ConvSeg& g, const ConvStep& st, int t, int c) {
-    const int s = st.token_seq[t], pos = st.positions[t], start = st.q_start[s];
-    const int hist = g.taps - 1;
-    float* srow = g.state + (size_t)st.slots[s] * g.state_stride + c;
-    float u[CONV_MAX_TAPS];
+// what a token's filters need to know of its sequence: looked up once per thread (or block)
+struct ConvToken {
+    int pos;        // the token's position
+    int avail;      // tokens of this step before it in its sequence: inputs further back come from the state
+    int slot;
+    int single;     // its sequence brings this token only: the filter moves the state on itself
+};
+__device__ __forceinline__ ConvToken conv_token(const ConvStep& st, int t) {
+    const int s = st.token_seq[t];
+    ConvToken m;
+    m.pos = st.positions[t];
+    m.avail = m.pos - st.q_start[s];
+    m.slot = st.slots[s];
+    m.single = st.cu_q[s + 1] - st.cu_q[s] == 1;
+    return m;
+}
+
+// the convolution of token t, channel c (the number of taps known at compile time: the loops unroll to straight
+// code); moves the state on if t is its sequence's only token
+template <int TAPS>
+__device__ __forceinline__ float conv_at(const ConvSeg& g, const ConvToken& m, int t, int c) {
+    constexpr int H = TAPS - 1;
+    const float* base = g.in + (size_t)t * g.in_stride + g.col0 + c;
+    float* srow = g.state + (size_t)m.slot * g.state_stride + c;
+    float u[TAPS];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-        if (j >= g.taps) break;
-        const int p = pos - hist + j;
+    for (int j = 0; j < TAPS; ++j) {
+        const int back = H - j;                                    // the input `back` positions before the token
         float v = 0.f;
-        if (p >= start) v = g.in[(size_t)(t - (pos - p)) * g.in_stride + g.col0 + c];
-        else if (p >= 0) v = srow[(size_t)(p - (start - hist)) * g.channels];
+        if (back <= m.avail) v = base[-(ptrdiff_t)back * g.in_stride];
+        else if (back <= m.pos) v = srow[(size_t)(H - (back - m.avail)) * g.channels];
         u[j] = v;
     }
     float acc = 0.f;
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-        if (j >= g.taps) break;
-        acc = fmaf(g.w[(size_t)c * g.taps + j], u[j], acc);
-    }
+    for (int j = 0; j < TAPS; ++j) acc = fmaf(g.w[(size_t)c * TAPS + j], u[j], acc);
     if (g.bias) acc += g.bias[c];
-    if (st.cu_q[s + 1] - st.cu_q[s] == 1) {
+    if (m.single) {
 #pragma unroll
-        for (int j = 1; j < CONV_MAX_TAPS; ++j) {
-            if (j >= g.taps) break;
-            srow[(size_t)(j - 1) * g.channels] = u[j];
-        }
+        for (int j = 1; j < TAPS; ++j) srow[(size_t)(j - 1) * g.channels] = u[j];
     }
     return acc;
 }
@@ -63,12 +75,13 @@ __device__ __forceinline__ float conv_at(const ConvSeg& g, const ConvStep& st, i
 __device__ __forceinline__ float silu_exact(float v) { return v / (1.0f + expf(-v)); }
 
 // out [N, channels] 32-bit; act: 0 none, 1 silu
+template <int TAPS>
 __global__ void __launch_bounds__(256) short_conv_kernel(ConvSeg g, ConvStep st, float* __restrict__ out, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x, t = blockIdx.x;
     if (c >= g.channels) return;
-    const float v = conv_at(g, st, t, c);
+    const float v = conv_at<TAPS>(g, conv_token(st, t), t, c);
     out[(size_t)t * g.channels + c] = act == 1 ? silu_exact(v) : v;
 }
 
@@ -84,18 +97,13 @@ struct ConvQkvArgs {
     const int* table; int table_stride;
 };
 
+template <int TAPS>
 __global__ void __launch_bounds__(256) conv_qkv_cache_kernel(ConvQkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ int place[2];
     const int t = blockIdx.x;
-    if (threadIdx.x == 0) {
-        const int pos = a.st.positions[t];
-        place[0] = a.table[(size_t)a.st.slots[a.st.token_seq[t]] * a.table_stride + pos / IDM_PAGE];
-        place[1] = pos % IDM_PAGE;
-    }
-    __syncthreads();
-    const size_t page = place[0], prow = place[1];
+    const ConvToken m = conv_token(a.st, t);                       // (one token per block: every thread the same)
+    const size_t page = a.table[(size_t)m.slot * a.table_stride + m.pos / IDM_PAGE], prow = m.pos % IDM_PAGE;
     const int qk_heads = a.n_q + a.n_kv;
     const int rest = a.dk - a.half;                       // work items of a q or k head: pairs, then single dims
     const int qk_items = qk_heads * rest, v_items = a.n_kv * a.dv;
@@ -105,19 +113,19 @@ __global__ void __launch_bounds__(256) conv_qkv_cache_kernel(ConvQkvArgs a) {
             T* dst = head < a.n_q ? a.q_out + ((size_t)t * a.n_q + head) * a.dk
                                   : a.k_pool + ((page * a.n_kv + (head - a.n_q)) * IDM_PAGE + prow) * (size_t)a.dk;
             if (r < a.half) {
-                const float u = conv_at(a.seg, a.st, t, head * a.dk + r);
-                const float v = conv_at(a.seg, a.st, t, head * a.dk + r + a.half);
+                const float u = conv_at<TAPS>(a.seg, m, t, head * a.dk + r);
+                const float v = conv_at<TAPS>(a.seg, m, t, head * a.dk + r + a.half);
                 const float2 cs = a.cs[(size_t)t * a.half + r];
                 from_f32(dst[r], u * cs.x - v * cs.y);
                 from_f32(dst[r + a.half], v * cs.x + u * cs.y);
             } else {
                 const int d = r + a.half;
-                from_f32(dst[d], conv_at(a.seg, a.st, t, head * a.dk + d));
+                from_f32(dst[d], conv_at<TAPS>(a.seg, m, t, head * a.dk + d));
             }
         } else {
             const int j = i - qk_items, g = j / a.dv, d = j % a.dv;
             T* dst = a.v_pool + ((page * a.n_kv + g) * IDM_PAGE + prow) * (size_t)a.dv;
-            from_f32(dst[d], conv_at(a.seg, a.st, t, qk_heads * a.dk + j));
+            from_f32(dst[d], conv_at<TAPS>(a.seg, m, t, qk_heads * a.dk + j));
         }
     }
 }
@@ -170,7 +178,10 @@ extern "C" int idm_short_conv(const float* in, int in_stride, int col0, int chan
     ConvSeg g;
     if (conv_seg(g, "short_conv", in, in_stride, col0, channels, taps, w, bias, state, state_stride)) return 1;
     ConvStep st{token_seq, positions, slots, q_start, cu_q};
-    idm_launch(short_conv_kernel, dim3(n_tokens, (channels + 255) / 256), dim3(256), 0, stream, g, st, out, act);
+    const dim3 grid(n_tokens, (channels + 255) / 256);
+#define CONV_GO(TAPS_) case TAPS_: idm_launch(short_conv_kernel<TAPS_>, grid, dim3(256), 0, stream, g, st, out, act); break;
+    switch (taps) { CONV_GO(1) CONV_GO(2) CONV_GO(3) CONV_GO(4) CONV_GO(5) CONV_GO(6) CONV_GO(7) CONV_GO(8) }
+#undef CONV_GO
     IDM_LAUNCH_CHECK("short_conv");
     return 0;
 }
@@ -190,7 +201,9 @@ extern "C" int idm_conv_qkv_cache(const float* in, int in_stride, int col0, int 
     a.st = ConvStep{token_seq, positions, slots, q_start, cu_q};
     a.n_q = n_q; a.n_kv = n_kv; a.dk = dk; a.dv = dv; a.half = half; a.cs = (const float2*)cs;
     a.q_out = (T*)q_out; a.k_pool = (T*)k_pool; a.v_pool = (T*)v_pool; a.table = table; a.table_stride = table_stride;
-    idm_launch(conv_qkv_cache_kernel, dim3(n_tokens), dim3(256), 0, stream, a);
+#define CONV_GO(TAPS_) case TAPS_: idm_launch(conv_qkv_cache_kernel<TAPS_>, dim3(n_tokens), dim3(256), 0, stream, a); break;
+    switch (taps) { CONV_GO(1) CONV_GO(2) CONV_GO(3) CONV_GO(4) CONV_GO(5) CONV_GO(6) CONV_GO(7) CONV_GO(8) }
+#undef CONV_GO
     IDM_LAUNCH_CHECK("conv_qkv_cache");
     return 0;
 }
