@@ -136,13 +136,17 @@ def _plain_left(x, w, s):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("variant", ["all", "bare", "whole_head", "wide_keys", "tensor_core_64", "tensor_core_128"])
+@pytest.mark.parametrize("variant", ["all", "bare", "whole_head", "wide_keys", "tensor_core_64", "tensor_core_128",
+                                     "tensor_core_64_long"])
 def test_sink_attention_alone_prompt_then_single_tokens(dtype, variant):
     """(Key and value rows of 64 or 128 elements take the tensor-core attention in bfloat16, which folds the sink
     behind the last run of keys; every other shape, and 32-bit, the general kernel.)"""
     spec = {"all": _sink_spec(),
             "tensor_core_64": _sink_spec(key_dim=64, value_dim=64, n_heads=4, n_kv_heads=2, softmax_scale=0.15,
                                          position=RotarySpec(3e4, 32, 1 << 20, variant="half_partial")),
+            # (more than 512 keys: several runs of key blocks, folded through scratch, the sink behind the last)
+            "tensor_core_64_long": _sink_spec(key_dim=64, value_dim=64, n_heads=4, n_kv_heads=1, softmax_scale=0.15,
+                                              position=RotarySpec(3e4, 32, 1 << 20, variant="half_partial")),
             "tensor_core_128": _sink_spec(key_dim=128, value_dim=128, n_heads=3, n_kv_heads=1, softmax_scale=0.1, gate=False,
                                           position=RotarySpec(3e4, 128, 1 << 20, variant="half_partial")),
             "bare": _sink_spec(conv_taps=1, position=None, sink=False, gate=False, n_kv_heads=6),
@@ -157,9 +161,9 @@ def test_sink_attention_alone_prompt_then_single_tokens(dtype, variant):
     part = cls(spec, w, "L.", rt)
     need = cls.cache_need(spec)
     assert need.key_row() == (spec.n_kv_heads, spec.key_dim) and need.value_row() == (spec.n_kv_heads, spec.value_dim)
-    cache = SequenceCache({0: need}, 64 * 8, DT[dtype], "cuda:0", max_seqs=2)
+    T, pre = (1300, 1291) if variant.endswith("long") else (140, 131)
+    cache = SequenceCache({0: need}, 64 * 24, DT[dtype], "cuda:0", max_seqs=2)
     slot = cache.alloc_slot()
-    T, pre = 140, 131
     x = (torch.randn(T, spec.hidden, generator=torch.Generator().manual_seed(3)) * 1.5).to(DT[dtype])
     ref = _plain_left(x.double(), _w64(w), spec)
     outs = []
