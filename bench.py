@@ -340,7 +340,7 @@ def kernel_times(lm, lens, seed: int):
     g = torch.Generator().manual_seed(seed)
     names = [n for n in dir(K) if not n.startswith("_") and callable(getattr(K, n)) and n not in
              ("scratch", "attention_tc_plan", "attention_tc_status", "gemm_status", "gemm_choices", "attention_tc_few_rows",
-              "tile_gate_up", "attention", "gemm", "wait_probe", "sample")]
+              "tile_gate_up", "attention", "gemm", "wait_probe", "sample", "attention_tc_fits", "ssd_chunks")]
     out, saved = {}, {n: getattr(K, n) for n in names}
     timing = [False]
 

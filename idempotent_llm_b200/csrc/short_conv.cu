@@ -72,16 +72,27 @@ __device__ __forceinline__ float conv_at(const ConvSeg& g, const ConvToken& m, i
     return acc;
 }
 
-__device__ __forceinline__ float silu_exact(float v) { return v / (1.0f + expf(-v)); }
+// silu of a filter's output: exact in the 32-bit library; with the hardware exponential and division where the
+// result is rounded to bfloat16 operands anyway (relative error ~1e-6)
+__device__ __forceinline__ float silu_exact(float v) {
+#if defined(IDM_F32)
+    return v / (1.0f + expf(-v));
+#else
+    return __fdividef(v, 1.0f + __expf(-v));
+#endif
+}
 
 // out [N, channels] 32-bit; act: 0 none, 1 silu
 template <int TAPS>
 __global__ void __launch_bounds__(256) short_conv_kernel(ConvSeg g, ConvStep st, float* __restrict__ out, int act) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ ConvToken token;                     // (one token per block: looked up by one thread)
     const int c = blockIdx.y * blockDim.x + threadIdx.x, t = blockIdx.x;
+    if (threadIdx.x == 0) token = conv_token(st, t);
+    __syncthreads();
     if (c >= g.channels) return;
-    const float v = conv_at<TAPS>(g, conv_token(st, t), t, c);
+    const float v = conv_at<TAPS>(g, token, t, c);
     out[(size_t)t * g.channels + c] = act == 1 ? silu_exact(v) : v;
 }
 
