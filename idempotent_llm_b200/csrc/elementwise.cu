@@ -384,6 +384,97 @@ __global__ void __launch_bounds__(256) post_pre_norm_kernel(float* __restrict__ 
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) from_f32(xr[c], vals[c] * inv * w_pre[c]);
 }
 
+// The same for rows of at most 4 * 256 elements with hidden % 4 == 0, in two forms that give the same bits: a block
+// per row (a thread owns four consecutive elements), and, for many rows, a warp per row in which lane l stands for
+// the block's threads l, l + 32, ..: it sums each of those warps by the same butterfly and adds the eight totals in
+// the same order.  Every product and sum is written out, so that the two forms cannot be contracted differently.
+struct PostPre4 { float4 y, h; };
+__device__ __forceinline__ float sumsq4(const float4& v) {
+    return __fmaf_rn(v.w, v.w, __fmaf_rn(v.z, v.z, __fmaf_rn(v.y, v.y, __fmul_rn(v.x, v.x))));
+}
+__device__ __forceinline__ float4 post_add4(const float4& h, const float4& y, float inv, const float4& w) {
+    return make_float4(__fmaf_rn(__fmul_rn(y.x, inv), w.x, h.x), __fmaf_rn(__fmul_rn(y.y, inv), w.y, h.y),
+                       __fmaf_rn(__fmul_rn(y.z, inv), w.z, h.z), __fmaf_rn(__fmul_rn(y.w, inv), w.w, h.w));
+}
+__device__ __forceinline__ void pre_store4(T* x, const float4& h, float inv, const float4& w, int mode) {
+    if (mode == 2) store4(x, h.x, h.y, h.z, h.w);
+    else store4(x, __fmul_rn(__fmul_rn(h.x, inv), w.x), __fmul_rn(__fmul_rn(h.y, inv), w.y), __fmul_rn(__fmul_rn(h.z, inv), w.z),
+                __fmul_rn(__fmul_rn(h.w, inv), w.w));
+}
+
+__global__ void __launch_bounds__(256) post_pre_norm_vec4_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                                                 const float* __restrict__ w_post, float eps,
+                                                                 const float* __restrict__ w_pre, float eps_pre,
+                                                                 T* __restrict__ x, int mode, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const size_t r = blockIdx.x;
+    const int c = threadIdx.x * 4;
+    const bool live = c < hidden;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 yv = live ? *reinterpret_cast<const float4*>(y + r * hidden + c) : zero;
+    float4 hv = live ? *reinterpret_cast<const float4*>(h + r * hidden + c) : zero;
+    float inv = 1.0f / sqrtf(block_sum(sumsq4(yv), scratch) / (float)hidden + eps);
+    if (live) {
+        hv = post_add4(hv, yv, inv, *reinterpret_cast<const float4*>(w_post + c));
+        *reinterpret_cast<float4*>(h + r * hidden + c) = hv;
+    }
+    if (mode == 0) return;
+    inv = mode == 1 ? 1.0f / sqrtf(block_sum(sumsq4(hv), scratch) / (float)hidden + eps_pre) : 0.f;
+    if (live) pre_store4(x + r * hidden + c, hv, inv, mode == 1 ? *reinterpret_cast<const float4*>(w_pre + c) : zero, mode);
+}
+
+__global__ void __launch_bounds__(256) post_pre_norm_rows_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                                                 const float* __restrict__ w_post, float eps,
+                                                                 const float* __restrict__ w_pre, float eps_pre,
+                                                                 T* __restrict__ x, int mode, int n_rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (i >= n_rows) return;
+    const size_t r = i;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 yv[8], hv[8];
+    float s[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const int c = (32 * w + lane) * 4;
+        yv[w] = c < hidden ? *reinterpret_cast<const float4*>(y + r * hidden + c) : zero;
+        hv[w] = c < hidden ? *reinterpret_cast<const float4*>(h + r * hidden + c) : zero;
+        s[w] = sumsq4(yv[w]);
+    }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s[w] = warp_sum(s[w]);
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += s[w];
+    float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const int c = (32 * w + lane) * 4;
+        if (c < hidden) {
+            hv[w] = post_add4(hv[w], yv[w], inv, *reinterpret_cast<const float4*>(w_post + c));
+            *reinterpret_cast<float4*>(h + r * hidden + c) = hv[w];
+        }
+        s[w] = sumsq4(hv[w]);
+    }
+    if (mode == 0) return;
+    if (mode == 1) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s[w] = warp_sum(s[w]);
+        total = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += s[w];
+        inv = 1.0f / sqrtf(total / (float)hidden + eps_pre);
+    }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const int c = (32 * w + lane) * 4;
+        if (c < hidden) pre_store4(x + r * hidden + c, hv[w], inv, mode == 1 ? *reinterpret_cast<const float4*>(w_pre + c) : zero, mode);
+    }
+}
+
 extern "C" int idm_post_pre_norm(float* h, const float* y, const float* w_post, float eps, const float* w_pre,
                                  float eps_pre, void* x, int mode, int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows == 0) return 0;
@@ -391,6 +482,17 @@ extern "C" int idm_post_pre_norm(float* h, const float* y, const float* w_post, 
     IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "post_pre_norm: hidden=%d does not fit shared memory", hidden);
     IDM_REQUIRE(mode == 0 || x != nullptr, "post_pre_norm: mode %d needs an output", mode);
     IDM_REQUIRE(mode != 1 || w_pre != nullptr, "post_pre_norm: mode 1 needs the next norm's weight");
+    if (hidden % 4 == 0 && hidden <= 1024) {
+        // which of the two runs depends on the number of rows; they give the same bits
+        if (n_rows >= 64)
+            idm_launch(post_pre_norm_rows_kernel, dim3((n_rows + 7) / 8), dim3(256), 0, stream, h, y, w_post, eps, w_pre, eps_pre,
+                       (T*)x, mode, n_rows, hidden);
+        else
+            idm_launch(post_pre_norm_vec4_kernel, dim3(n_rows), dim3(256), 0, stream, h, y, w_post, eps, w_pre, eps_pre, (T*)x,
+                       mode, hidden);
+        IDM_LAUNCH_CHECK("post_pre_norm");
+        return 0;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(post_pre_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

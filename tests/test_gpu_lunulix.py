@@ -278,6 +278,26 @@ def test_norm_behind_and_in_front_in_one_pass(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [96, 1024])
+def test_norm_behind_and_in_front_gives_a_row_the_same_bits_in_any_step(dtype, hidden):
+    """Rows of up to 1024 elements take a block per row in small steps and a warp per row in large ones: the same
+    bits for a row either way, and the plain implementation's values."""
+    K = _rt(dtype).kernels
+    g = torch.Generator().manual_seed(5)
+    h0, y = torch.randn(90, hidden, generator=g), torch.randn(90, hidden, generator=g) * 2
+    wp, wn = torch.rand(hidden, generator=g) + 0.5, torch.rand(hidden, generator=g) + 0.5
+    outs = {}
+    for rows in (90, 9):
+        h = h0[:rows].clone().cuda()
+        x = K.post_pre_norm(h, y[:rows].contiguous().cuda(), wp.cuda(), 1e-5, w_pre=wn.cuda(), eps_pre=1e-5)
+        outs[rows] = (h.cpu(), x.float().cpu())
+    assert torch.equal(outs[90][0][:9], outs[9][0]) and torch.equal(outs[90][1][:9], outs[9][1])
+    want_h = h0.double() + plain.rms_norm(y.double(), wp.double(), 1e-5)
+    assert (outs[90][0].double() - want_h).abs().max() < 1e-5
+    assert helpers.rel_err(outs[90][1], plain.rms_norm(want_h, wn.double(), 1e-5)) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_gelu_gate_in_the_product_and_alone(dtype):
     """The tanh form of gelu as the epilogue of the gate/up product (bfloat16) and as a kernel of its own."""
     from idempotent_llm_b200.config.specs import GatedMLPNames, GatedMLPSpec
