@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(256) conv_qkv_cache_kernel(ConvQkvArgs a) {
     const int qk_heads = a.n_q + a.n_kv;
     const int rest = a.dk - a.half;                       // work items of a q or k head: pairs, then single dims
     const int qk_items = qk_heads * rest, v_items = a.n_kv * a.dv;
-    for (int i = threadIdx.x; i < qk_items + v_items; i += blockDim.x) {
+    // (steps of few tokens spread a token's items over several blocks: gridDim.y)
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < qk_items + v_items; i += gridDim.y * blockDim.x) {
         if (i < qk_items) {
             const int head = i / rest, r = i % rest;
             T* dst = head < a.n_q ? a.q_out + ((size_t)t * a.n_q + head) * a.dk
@@ -212,7 +213,13 @@ extern "C" int idm_conv_qkv_cache(const float* in, int in_stride, int col0, int 
     a.st = ConvStep{token_seq, positions, slots, q_start, cu_q};
     a.n_q = n_q; a.n_kv = n_kv; a.dk = dk; a.dv = dv; a.half = half; a.cs = (const float2*)cs;
     a.q_out = (T*)q_out; a.k_pool = (T*)k_pool; a.v_pool = (T*)v_pool; a.table = table; a.table_stride = table_stride;
-#define CONV_GO(TAPS_) case TAPS_: idm_launch(conv_qkv_cache_kernel<TAPS_>, dim3(n_tokens), dim3(256), 0, stream, a); break;
+    // a block per token; with few tokens, several blocks per token, so that two blocks' worth of work per SM is about
+    const int items = (n_q + n_kv) * (dk - half) + n_kv * dv;
+    int split = (296 + n_tokens - 1) / n_tokens;
+    if (split > (items + 255) / 256) split = (items + 255) / 256;
+    if (split < 1) split = 1;
+    const dim3 grid(n_tokens, split);
+#define CONV_GO(TAPS_) case TAPS_: idm_launch(conv_qkv_cache_kernel<TAPS_>, grid, dim3(256), 0, stream, a); break;
     switch (taps) { CONV_GO(1) CONV_GO(2) CONV_GO(3) CONV_GO(4) CONV_GO(5) CONV_GO(6) CONV_GO(7) CONV_GO(8) }
 #undef CONV_GO
     IDM_LAUNCH_CHECK("conv_qkv_cache");
