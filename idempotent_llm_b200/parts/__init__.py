@@ -1,7 +1,7 @@
 """Parts a layer is put together from: norm, position encoding, mixer, feed-forward, block."""
 
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, FeedForward, Mixer, Norm,
-                   Part, PositionEncoding, Runtime)
+                   NormedDelta, Part, PositionEncoding, Runtime)
 from .norm import RMSNorm
 from .rotary import Rotary
 from .attention import GQAAttention
@@ -13,5 +13,5 @@ from .parallel import ParallelMixer
 from .sandwich import SandwichBlock, TokenSide
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "FeedForward", "Mixer",
-           "Norm", "Part", "PositionEncoding", "Runtime", "RMSNorm", "Rotary", "GQAAttention",
+           "Norm", "NormedDelta", "Part", "PositionEncoding", "Runtime", "RMSNorm", "Rotary", "GQAAttention",
            "GatedMLP", "PreNormBlock", "SinkAttention", "SSDMixer", "ParallelMixer", "SandwichBlock", "TokenSide"]

@@ -68,6 +68,18 @@ class Runtime:
         return t
 
 
+class NormedDelta:
+    """A pending delta that is normed before it is added: ``h += y / sqrt(mean(y^2) + eps) * weight``.  A block that
+    ends with a norm behind its last sublayer may hand this on instead of adding it itself, so that the next
+    block's first norm does both in one pass over the row; any other consumer calls ``add_into`` first."""
+
+    def __init__(self, y, weight, eps: float):
+        self.y, self.weight, self.eps = y, weight, eps
+
+    def add_into(self, h, kernels) -> None:
+        kernels.post_pre_norm(h, self.y, self.weight, self.eps)
+
+
 class Part:
     # False for a part that synchronises with the host inside ``forward`` (reads device values):
     # a model with such a part runs its single-token steps without CUDA graphs.

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.loader import TensorDecl
-from .base import NORMS, Norm
+from .base import NORMS, Norm, NormedDelta
 
 
 @NORMS.register("rmsnorm")
@@ -27,6 +27,12 @@ class RMSNorm(Norm):
         self.weight = weights[prefix + spec.weight].to(torch.float32).contiguous()
 
     def forward(self, h, delta, ctx, rows=None):
+        if isinstance(delta, NormedDelta):
+            if rows is None:                      # the norm behind the last sublayer and this one in one pass
+                return self.rt.kernels.post_pre_norm(h, delta.y, delta.weight, delta.eps, w_pre=self.weight,
+                                                     eps_pre=self.spec.eps)
+            delta.add_into(h, self.rt.kernels)
+            delta = None
         return self.rt.kernels.add_rmsnorm(h, delta, self.weight, self.spec.eps, rows=rows)
 
     def emit(self, prog, h, out, rows=False):

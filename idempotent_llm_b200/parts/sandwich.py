@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.loader import TensorDecl
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Part
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, NormedDelta, Part
 from .mlp import ACTIVATIONS
 
 
@@ -92,9 +92,8 @@ class SandwichBlock(Block):
             pre = self.feed_forward_norm
             x = K.post_pre_norm(h, y, post.weight, post.spec.eps, w_pre=pre.weight, eps_pre=pre.spec.eps)
             y, post = self.feed_forward.forward(x, ctx)[0], self.feed_forward_post_norm
+        # the norm behind the last sublayer is handed on: the next layer's first norm (or the final one) adds it
         if self.token_side is not None:
             x = K.post_pre_norm(h, y, post.weight, post.spec.eps, cast=True)
-            K.post_pre_norm(h, self.token_side.forward(x, ctx), self.token_side.norm, self.token_side.spec.eps)
-        else:
-            K.post_pre_norm(h, y, post.weight, post.spec.eps)
-        return h, None
+            return h, NormedDelta(self.token_side.forward(x, ctx), self.token_side.norm, self.token_side.spec.eps)
+        return h, NormedDelta(y, post.weight, post.spec.eps)

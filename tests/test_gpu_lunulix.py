@@ -353,7 +353,10 @@ def test_whole_prompt_and_every_layer_against_plain(lunulix_dirs, name, dtype):
     def recording(inner):
         def forward(h, *a, **k):
             out = inner(h, *a, **k)
-            seen.append(out[0].clone())
+            after = out[0].clone()
+            if out[1] is not None:                   # the normed delta of the layer's last sublayer, handed on
+                out[1].add_into(after, lm.model.rt.kernels)
+            seen.append(after)
             return out
         return forward
     for b in lm.model.blocks:
