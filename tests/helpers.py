@@ -148,6 +148,32 @@ LUNULIX = {
 }
 
 
+def lunulix_random_config(seed: int) -> dict:
+    """A Lunulix configuration drawn from sizes a model of the design may have: one to three unlike layers, grouped
+    and ungrouped heads, key and value widths that differ or not (64 and 128 among them: the tensor-core attention),
+    rotation of none, part or all of a head with or without scaling, filters of 0 to 4 taps, state sizes of 16 to 256,
+    norm parts, layers without feed-forward, with or without the token side input."""
+    import random
+    r = random.Random(seed)
+
+    def layer():
+        kv = r.choice([1, 2, 4]); heads = kv * r.choice([1, 2, 3, 4])
+        dim = r.choice([32, 48, 64, 64, 128, 96]); vdim = r.choice([dim, dim, 32, 64, 80])
+        rot = r.choice([0, dim // 2, dim, 16])
+        scaling = r.choice([None, (8.0, 1.0, 4.0, 2048), (2.0, 0.5, 8.0, 512), (32.0, 1.0, 4.0, 64)])
+        r_heads = r.choice([2, 4, 6, 8]); groups = r.choice([g for g in (1, 2, r_heads) if r_heads % g == 0])
+        r_vdim = r.choice([16, 32, 48, 64, 128]); state = r.choice([16, 32, 48, 64, 128, 256])
+        parts = r.choice([g for g in (1, 2, 4, r_heads, 8) if (r_heads * r_vdim) % g == 0])
+        return lunulix_layer(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=r.choice([dim ** -0.5, 0.1, 0.05]),
+                             lconv=r.choice([0, 2, 3, 4]), rot_dims=rot, rot_base=r.choice([1e4, 2.5e5, 1e6]),
+                             scaling=scaling if rot else None, r_heads=r_heads, r_vdim=r_vdim, state=state, groups=groups,
+                             rconv=r.choice([2, 3, 4]), norm_groups=parts, left_scale=r.choice([1.0, 0.6, 0.3]),
+                             right_scale=r.choice([1.0, 0.9, 1.5]), ff=r.choice([None, 64, 160, 256]))
+    width = r.choice([64, 96, 128, 256, 320])
+    return lunulix_config([layer() for _ in range(r.choice([1, 2, 3]))], vocab=r.choice([128, 500, 1000]), width=width,
+                          emb_scale=r.choice([1.0, 4.0, 16.0]), eps=r.choice([1e-5, 1e-6]), side_dim=r.choice([0, 8, 16, 32]))
+
+
 def make_lunulix_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.15, edit=None) -> str:
     """A Lunulix model folder with seeded random weights; ``edit(name, tensor) -> tensor`` may change them."""
     from idempotent_llm_b200.config import LunulixConfig

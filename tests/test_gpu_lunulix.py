@@ -506,6 +506,27 @@ def test_long_decoding_of_a_batch(lunulix_dirs, dtype, graph):
         assert _close(last[row:row + 1], _plain_logits(d, f)[-1:], dtype)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_drawn_configurations_in_a_batch_and_decoding(tmp_path, seed):
+    """Configurations drawn at random (sizes, head counts, filters, rotations, state sizes, layer make-up): a prompt of
+    200 tokens beside a short one, then six single tokens each, in both types."""
+    cfg = helpers.lunulix_random_config(seed)
+    d = helpers.make_lunulix_dir(cfg, str(tmp_path), seed=seed, std=0.08)
+    V = cfg["vocab"]
+    a, b = helpers.rand_ids(206, V, seed), helpers.rand_ids(9, V, seed + 100)
+    want_a, want_b = _plain_logits(d, a), _plain_logits(d, b)
+    for dtype in ("float32", "bfloat16"):
+        lm = api.load(d, dtype=dtype, max_tokens=512)
+        sa, sb = lm.engine.open(), lm.engine.open()
+        g = lm.engine.step([(sa, a[:200]), (sb, b[:3])], [list(range(200)), [0, 1, 2]])
+        ga, gb = [g[:200]], [g[200:]]
+        for k in range(6):
+            g = lm.engine.step([(sa, [a[200 + k]]), (sb, [b[3 + k]])])
+            ga.append(g[0:1]); gb.append(g[1:2])
+        assert _close(torch.cat(ga), want_a, dtype) and _close(torch.cat(gb), want_b, dtype), f"{dtype}: {cfg}"
+        del lm
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(lunulix_dirs, dtype):
     """``LM.generate`` (scheduler, batching, sampling) against greedy decoding with the plain implementation."""
