@@ -28,9 +28,11 @@ class RotarySpec:
     twice (not interleaved); pairs are ``(d, d + dim / 2)``
     (reference: src/detllm/ops/rope.py:25-35, 47-55).  ``variant`` names how the
     rotation sits in a head, which the mixer's kernels must have:
-    ``"half_whole_head"`` (``dim`` = the head size, pairs half a head apart) is the
-    one built; a partial rotation (``dim`` < head size) or interleaved pairs would
-    be other variants, refused by name until a kernel has them.
+    ``"half_whole_head"`` (``dim`` = the head size, pairs half a head apart),
+    ``"half_partial"`` (the first ``dim`` dims of a head, pairs ``dim / 2`` apart) and
+    ``"interleaved"`` (neighbours ``(2 j, 2 j + 1)`` turned by angle ``j``) are built, each by
+    the mixers that name it; any other is refused by name.  ``scaling`` rescales the
+    frequencies (``WavelengthScaling`` or ``RampScaling``).
     """
 
     theta: float
@@ -52,6 +54,32 @@ class WavelengthScaling:
     low: float
     high: float
     original: float
+
+
+@dataclass(frozen=True)
+class RampScaling:
+    """Frequencies slowed down along a ramp over the index j (a stretch of the trained length ``original`` by
+    ``factor``).  With ``at(n) = dim * ln(original / (2 pi n)) / (2 ln theta)`` the index whose wave makes ``n`` turns
+    over the trained length, ``lo = max(floor(at(fast)), 0)``, ``hi = min(ceil(at(slow)), dim - 1)`` and ``s_j =
+    clamp((j - lo) / max(hi - lo, 0.001), 0, 1)``, the frequency is ``s_j f_j / factor + (1 - s_j) f_j``; cos and sin
+    are multiplied by ``0.1 ln(factor) + 1``."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
+class DyTNormSpec:
+    """A norm without statistics: ``tanh(alpha x) * w + b`` element by element, ``alpha`` one learned number.  The
+    tensors are ``prefix + weight``, that name plus ``alpha_suffix`` and plus ``bias_suffix``."""
+
+    size: int
+    weight: str = "weight"
+    alpha_suffix: str = ".alpha"
+    bias_suffix: str = ".b"
+    kind: str = "dyt"
 
 
 @dataclass(frozen=True)
@@ -123,6 +151,80 @@ class GatedMLPSpec:
     names: GatedMLPNames
     activation: str = "silu"
     kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class LatentAttentionNames:
+    """Checkpoint names of a latent attention's tensors, behind the mixer's prefix."""
+
+    q: str = "q"
+    down: str = "dkv"
+    down_norm: str = "dkv.norm"
+    up_k: str = "uk"
+    up_v: str = "uv"
+    o: str = "o"
+    sink: str = "sink"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are made from one latent vector per token (a *mixer*).
+
+    A head's query has ``plain_dim`` unrotated dims followed by ``rot_dim`` rotated ones.  The down projection
+    gives ``kv_rank + rot_dim`` numbers per token: the first ``kv_rank``, divided by their root mean square (``eps``
+    inside the root) and multiplied by a weight, are the latent ``c``; the last ``rot_dim``, rotated, are a key part
+    all heads share.  Head h's unrotated key is ``Uk_h c`` and its value ``Uv_h c`` (``value_dim`` numbers); the score
+    is ``(q_plain . k_plain + q_rot . k_rot) * softmax_scale``.  ``position`` (variant ``"interleaved"``) turns the
+    first ``position.dim`` of the rotated dims.  ``sink``: one learned score per head joins the softmax's
+    denominator with no key and no value.  Only ``c`` and the rotated key part are kept per token."""
+
+    hidden: int
+    n_heads: int
+    plain_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    softmax_scale: float
+    eps: float
+    position: Optional[RotarySpec] = None
+    sink: bool = False
+    names: LatentAttentionNames = LatentAttentionNames()
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DenseMLPNames:
+    up: str = "up"
+    down: str = "down"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """Feed-forward without a gate: ``down(act(up(x)))``; ``activation`` ``"relu2"`` is the square of relu."""
+
+    hidden: int
+    intermediate: int
+    activation: str = "relu2"
+    names: DenseMLPNames = DenseMLPNames()
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
+class TableExpertsSpec:
+    """``n_experts`` small gated feed-forwards ``down_e(act(gate_e x) * up_e x)`` of which a token uses ``top``, named by
+    a table ``[vocab_size, top]`` of integers indexed by the token's id (no learned router), each with weight
+    ``1 / top``.  Expert e's tensors are ``prefix + expert.format(e) + gate / up / down``."""
+
+    hidden: int
+    intermediate: int
+    n_experts: int
+    top: int
+    vocab_size: int
+    activation: str = "silu"
+    table: str = "table"
+    expert: str = "e{}."
+    names: GatedMLPNames = GatedMLPNames(gate="gate", up="up", down="down")
+    kind: str = "table_experts"
 
 
 @dataclass(frozen=True)
@@ -266,9 +368,9 @@ class LayerSpec:
 
     prefix: str
     mixer: object
-    feed_forward: object
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward: object                # None: the layer has no feed-forward (then no second norm either)
+    mixer_norm: object
+    feed_forward_norm: object
     mixer_norm_prefix: str
     feed_forward_norm_prefix: str
     kind: str = "prenorm"
@@ -281,12 +383,16 @@ class RunEntry:
     ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice).
     ``cache`` names the cache entry the mixer uses; entries that share a
     number share keys and values.  ``writes_cache`` is False for a mixer that
-    only reads what an earlier entry wrote.
+    only reads what an earlier entry wrote.  ``mix_in``: before this stop the
+    stream is replaced by ``M [stream ; embedding output]`` with the model's
+    ``ModelSpec.mix_in_name`` matrix ``[hidden, 2 hidden]`` (the opening of a
+    pass over layers that run several times).
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
+    mix_in: bool = False
 
 
 @dataclass(frozen=True)
@@ -305,6 +411,9 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02
     embed_scale: float = 1.0            # the embedding row is multiplied with this constant
+    mix_in_name: Optional[str] = None   # the matrix of the schedule's `mix_in` stops
+    logit_scale: float = 1.0            # logits are multiplied with this constant, then
+    logit_softcap: Optional[float] = None   # capped: cap * tanh(logits / cap)
     extra: dict = field(default_factory=dict, compare=False)
 
     def __post_init__(self):
@@ -319,6 +428,8 @@ class ModelSpec:
                 seen_writer.add(e.cache)
             elif e.cache not in seen_writer:
                 raise ConfigError(f"schedule entry reads cache {e.cache} before anything wrote it")
+            if e.mix_in and not self.mix_in_name:
+                raise ConfigError("a schedule entry mixes the embedding in, but the model names no matrix for it")
 
 
 def default_schedule(n_layers: int) -> Tuple[RunEntry, ...]:

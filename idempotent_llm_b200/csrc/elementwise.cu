@@ -579,3 +579,99 @@ extern "C" int idm_gate_scale(const void* o, const float* gate, int gate_stride,
     IDM_LAUNCH_CHECK("gate_scale");
     return 0;
 }
+
+// ------------------------------------------------------- residual add + a norm without statistics
+// The same interface as add_rmsnorm (rows == nullptr: h[r] += sum_p delta[p][r], stored, x[r] = f(h[r]); rows given:
+// only those rows, nothing stored) with f(v) = tanh(alpha v) * w + b, element by element, in 32-bit.
+__global__ void __launch_bounds__(256) add_dyt_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                                      size_t partial_stride, const float* __restrict__ w,
+                                                      const float* __restrict__ b, float alpha, T* __restrict__ x,
+                                                      const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* hr = h + (size_t)r * hidden;
+    T* xr = x + (size_t)i * hidden;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
+        const float v = add_partials(hr[c], delta, n_partials, partial_stride, (size_t)r * hidden + c);
+        if (!rows && n_partials) hr[c] = v;
+        from_f32(xr[c], fmaf(tanhf(alpha * v), w[c], b[c]));
+    }
+}
+
+extern "C" int idm_add_dyt(float* h, const float* delta, int n_partials, long long partial_stride, const float* w,
+                           const float* b, float alpha, void* x, const int* rows, int n_rows, int hidden,
+                           cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_dyt: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    // few rows: a row's elements over several blocks (nothing is summed over a row, so the split changes no value)
+    const int by = n_rows >= 128 ? 1 : max(1, min((hidden + 255) / 256, 128 / n_rows));
+    idm_launch(add_dyt_kernel, dim3(n_rows, by), dim3(256), 0, stream, h, delta, delta ? n_partials : 0, (size_t)partial_stride,
+               w, b, alpha, (T*)x, rows, hidden);
+    IDM_LAUNCH_CHECK("add_dyt");
+    return 0;
+}
+
+// ------------------------------------------------------- an activation of one argument, 32-bit in, storage type out
+// act 2: relu(z)^2
+__global__ void __launch_bounds__(256) act_cast_kernel(const float* __restrict__ z, T* __restrict__ y, size_t n, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(z[i], 0.f);
+    from_f32(y[i], v * v);
+}
+
+extern "C" int idm_act_cast(const float* z, void* y, long long n, int act, cudaStream_t stream) {
+    if (n == 0) return 0;
+    IDM_REQUIRE(act == 2, "act_cast: activation %d is not built (2: the square of relu)", act);
+    idm_launch(act_cast_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, z, (T*)y, (size_t)n, act);
+    IDM_LAUNCH_CHECK("act_cast");
+    return 0;
+}
+
+// ------------------------------------------------------- the stream and a second stream side by side
+// h[r] += sum_p delta[p][r] (stored), out[r] = [h[r] | x0[r]] in the storage type: the input of a product that
+// mixes the running stream with an earlier one.
+__global__ void __launch_bounds__(256) concat_cast_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                                          size_t partial_stride, const float* __restrict__ x0,
+                                                          T* __restrict__ out, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = add_partials(h[r * hidden + c], delta, n_partials, partial_stride, r * hidden + c);
+        if (n_partials) h[r * hidden + c] = v;
+        from_f32(out[r * 2 * hidden + c], v);
+        from_f32(out[r * 2 * hidden + hidden + c], x0[r * hidden + c]);
+    }
+}
+
+extern "C" int idm_concat_cast(float* h, const float* delta, int n_partials, long long partial_stride, const float* x0,
+                               void* out, int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    idm_launch(concat_cast_kernel, dim3(n_rows), dim3(256), 0, stream, h, delta, delta ? n_partials : 0, (size_t)partial_stride, x0,
+               (T*)out, hidden);
+    IDM_LAUNCH_CHECK("concat_cast");
+    return 0;
+}
+
+// ------------------------------------------------------- logits times a constant, then a soft cap
+// l <- cap * tanh(l * scale / cap)  (cap <= 0: l * scale alone), in place
+__global__ void __launch_bounds__(256) logit_cap_kernel(float* __restrict__ l, size_t n, float scale, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = l[i] * scale;
+    l[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+extern "C" int idm_logit_cap(float* logits, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    idm_launch(logit_cap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, logits, (size_t)n, scale, cap);
+    IDM_LAUNCH_CHECK("logit_cap");
+    return 0;
+}

@@ -13,7 +13,7 @@ import torch
 
 from ..cache.spec import CacheNeed
 from ..config.specs import ModelSpec
-from ..parts.base import BLOCKS, MIXERS, NORMS, Runtime
+from ..parts.base import BLOCKS, MIXERS, NORMS, NormedDelta, Runtime
 from ..weights.loader import TensorDecl
 
 
@@ -22,6 +22,8 @@ def declare_weights(spec: ModelSpec) -> List[TensorDecl]:
     for layer in spec.layers:
         decls += BLOCKS.get(layer.kind).declare(layer)
     decls += NORMS.get(spec.final_norm.kind).declare(spec.final_norm, spec.final_norm_prefix)
+    if spec.mix_in_name:
+        decls.append(TensorDecl(spec.mix_in_name, (spec.hidden, 2 * spec.hidden)))
     # tied: an lm_head in the file is tolerated and ignored; untied: it is required
     decls.append(TensorDecl(spec.head_name, (spec.vocab_size, spec.hidden), optional=spec.tie_embeddings))
     # a tensor that several parts share (a table all layers read) is declared by each of them, alike
@@ -60,6 +62,7 @@ class CausalLM:
         self.blocks = [BLOCKS.get(layer.kind)(layer, weights, layer.prefix, rt) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, weights,
                                                           spec.final_norm_prefix, rt)
+        self.mix_in = weights[spec.mix_in_name].to(rt.dtype).contiguous() if spec.mix_in_name else None
         self._programs = {}
         self.graph_safe = all(getattr(part, "graph_safe", True) for b in self.blocks
                               for part in vars(b).values())
@@ -82,6 +85,8 @@ class CausalLM:
         try:
             if float(getattr(self.spec, "embed_scale", 1.0)) != 1.0:
                 raise NotProgrammable("a scaled embedding is called from forward")
+            if self.mix_in is not None or self.spec.logit_scale != 1.0 or self.spec.logit_softcap:
+                raise NotProgrammable("a stream mixed with the embedding, or scaled and capped logits, are called from forward")
             prog = StepProgram(K)
             h = prog.buffer("stream", per_token=4 * hidden)
             prog.embed(self.embed, h)
@@ -111,11 +116,22 @@ class CausalLM:
         scale = float(getattr(self.spec, "embed_scale", 1.0))
         h = K.embed(ctx.tokens, self.embed) if scale == 1.0 else K.embed_scaled(ctx.tokens, self.embed, scale)
         pending = None
+        pad = {"pad": True} if self.spec.hidden % 8 else {}
+        x0 = h.clone() if self.mix_in is not None else None         # the embedding output, kept for the mixes
         for e in self.spec.schedule:
+            if e.mix_in:
+                # the stream (what is pending added first) and the embedding output side by side, times one matrix
+                if isinstance(pending, NormedDelta):
+                    pending.add_into(h, K)
+                    pending = None
+                h, pending = K.gemm_store(K.concat_cast(h, pending, x0), self.mix_in, **pad), None
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, cache.view(e.cache),
                                                       cache.state_of(e.cache), e.writes_cache)
         x = self.final_norm.forward(h, pending, ctx, rows=want_rows)
-        return K.gemm_store(x, self.head, **({"pad": True} if self.spec.hidden % 8 else {}))
+        logits = K.gemm_store(x, self.head, **pad)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap:
+            K.logit_cap(logits, self.spec.logit_scale, self.spec.logit_softcap or 0.0)
+        return logits
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0

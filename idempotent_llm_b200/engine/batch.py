@@ -32,6 +32,8 @@ class StepContext:
     host_q_lens: List[int]
     host_slots: List[int]
     host_starts: List[int]
+    host_tokens: object = None   # the step's token ids per sequence on the host, where the caller has them (None in
+                                 # steps whose tokens exist on the device only: a device-side decode loop)
     memo: Dict = field(default_factory=dict)   # per-step shared tables (position encodings)
 
 
@@ -100,7 +102,7 @@ def advance_packed_single(buf: np.ndarray, n_seq: int, tokens: Sequence[int]) ->
 
 
 def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens: List[int],
-                        starts: List[int], max_kv_len=None) -> StepContext:
+                        starts: List[int], max_kv_len=None, host_tokens=None) -> StepContext:
     n_seq = len(slots)
     lay = PackedLayout(n, n_seq)
     return StepContext(
@@ -112,4 +114,4 @@ def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens:
         max_q_len=max(q_lens) if q_lens else 0,
         max_kv_len=max_kv_len if max_kv_len is not None else max(s + q for s, q in zip(starts, q_lens)),
         single_token=all(q == 1 for q in q_lens),
-        host_q_lens=list(q_lens), host_slots=list(slots), host_starts=list(starts))
+        host_q_lens=list(q_lens), host_slots=list(slots), host_starts=list(starts), host_tokens=host_tokens)

@@ -233,7 +233,7 @@ class Engine:
                     else logits[:0].clone()
         else:
             dev = self._upload(full)
-            ctx = context_from_packed(dev, n, slots, q_lens, starts)
+            ctx = context_from_packed(dev, n, slots, q_lens, starts, host_tokens=toks)
             logits = self.model.forward(ctx, self.cache, dev[full.numel() - len(rows):])
         for s, st, t in zip(slots, starts, toks):
             self.cache.set_length(s, st + len(t))

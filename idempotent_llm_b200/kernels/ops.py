@@ -92,6 +92,18 @@ SIGNATURES = {
     "idm_gate_scale": (c_int, "ppifpiiiip"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_attention_tc_set_few_rows": (c_int, "i"),
+    "idm_latent_kv_finish": (c_int, "piiiiipfpifppippppip"),
+    "idm_headwise": (c_int, "pqiipipiqiiipifiip"),
+    "idm_latent_attention_max_rank": (c_int, ""),
+    "idm_latent_attention": (c_int, "pppippppppiiiifiip"),
+    "idm_experts_from_table": (c_int, "ppipip"),
+    "idm_experts_few": (c_int, "pppppppiiiiiifp"),
+    "idm_rows_gather": (c_int, "pppiip"),
+    "idm_experts_combine": (c_int, "pppiiifp"),
+    "idm_add_dyt": (c_int, "ppiqppfppiip"),
+    "idm_act_cast": (c_int, "ppqip"),
+    "idm_concat_cast": (c_int, "ppiqppiip"),
+    "idm_logit_cap": (c_int, "pqffp"),
     "idm_gemm_f32": (c_int, "pppiiip"),
     "idm_gemm_set_small": (None, "iii"),
     "idm_gemm_set_small_max": (None, "i"),
@@ -778,6 +790,157 @@ class Kernels:
     def gemm_status(self) -> int:
         """0, or 1 if a bounded wait inside the tensor-core GEMM ran out since the last call (synchronises)."""
         return 0 if self.dtype == torch.float32 else self.lib.idm_gemm_status()
+
+    # ---- a norm without statistics, one-argument activations, streams side by side, capped logits ----
+    def _delta_args(self, delta, n, hidden):
+        if delta is None:
+            return None, 0, 0
+        self._need(delta, torch.float32, "delta")
+        if delta.dim() != 3 or tuple(delta.shape[1:]) != (n, hidden):
+            raise KernelError(f"delta {tuple(delta.shape)} does not match the stream {(n, hidden)}")
+        return delta.data_ptr(), delta.shape[0], n * hidden
+
+    def add_dyt(self, h, delta, w, b, alpha: float, rows=None) -> torch.Tensor:
+        """``h += delta`` (in place, unless ``rows`` selects rows), then ``tanh(alpha h) * w + b`` in the storage dtype."""
+        self._need(h, torch.float32, "residual stream")
+        self._need(w, torch.float32, "norm weight")
+        self._need(b, torch.float32, "norm bias")
+        n, hidden = h.shape
+        if w.numel() != hidden or b.numel() != hidden:
+            raise KernelError(f"norm weight and bias have {w.numel()}, {b.numel()} elements, rows have {hidden}")
+        dp, P, stride = self._delta_args(delta, n, hidden)
+        if rows is not None:
+            self._need(rows, torch.int32, "rows")
+        n_out = n if rows is None else rows.numel()
+        x = torch.empty((n_out, hidden), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_add_dyt(_p(h), dp, P, stride, _p(w), _p(b), float(alpha), _p(x), _p(rows), n_out, hidden,
+                                         self._stream()))
+        return x
+
+    def act_cast(self, z: torch.Tensor, act: int) -> torch.Tensor:
+        """An activation of one argument over a 32-bit product, in the storage dtype (``act`` 2: relu squared)."""
+        self._need(z, torch.float32, "activation input")
+        y = torch.empty(z.shape, dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_act_cast(_p(z), _p(y), z.numel(), act, self._stream()))
+        return y
+
+    def concat_cast(self, h, delta, x0) -> torch.Tensor:
+        """``h += delta`` in place, then ``[h | x0]`` in the storage dtype ``[N, 2 * hidden]``."""
+        self._need(h, torch.float32, "residual stream")
+        self._need(x0, torch.float32, "second stream")
+        n, hidden = h.shape
+        if tuple(x0.shape) != (n, hidden):
+            raise KernelError(f"streams {tuple(h.shape)} and {tuple(x0.shape)} differ")
+        dp, P, stride = self._delta_args(delta, n, hidden)
+        out = torch.empty((n, 2 * hidden), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_concat_cast(_p(h), dp, P, stride, _p(x0), _p(out), n, hidden, self._stream()))
+        return out
+
+    def logit_cap(self, logits: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+        """In place: ``cap * tanh(logits * scale / cap)`` (``cap`` 0: the constant alone)."""
+        self._need(logits, torch.float32, "logits")
+        self._check(self.lib.idm_logit_cap(_p(logits), logits.numel(), float(scale), float(cap or 0.0), self._stream()))
+        return logits
+
+    # ---- attention through a latent -----------------------------------------------------------------
+    def latent_max_rank(self) -> int:
+        return int(self.lib.idm_latent_attention_max_rank())
+
+    def latent_kv_finish(self, proj, col0: int, rank: int, rot_dim: int, rot_dims: int, w_norm, eps: float, cs, mag: float,
+                         kv, ctx, keep_rows: bool = False):
+        """Columns ``[col0, col0 + rank + rot_dim)`` of the 32-bit ``proj``: the first ``rank`` normed (one root mean
+        square, times ``w_norm``), the rest turned by the step's table ``cs [N, half, 2]``; the row goes to the
+        token's place in the cache entry and, with ``keep_rows``, is also returned packed ``[N, rank + rot_dim]``."""
+        self._need(proj, torch.float32, "projection")
+        n, ld = proj.shape
+        D = rank + rot_dim
+        if kv.k.dtype != self.dtype or tuple(kv.k.shape[1:]) != (1, self.page, D) or not kv.k.is_contiguous():
+            raise KernelError(f"cache entry {tuple(kv.k.shape)} {kv.k.dtype} does not fit [pages, 1, {self.page}, {D}]")
+        half = 0 if cs is None else cs.shape[1]
+        rows = torch.empty((n, D), dtype=self.dtype, device=self.device) if keep_rows else None
+        self._check(self.lib.idm_latent_kv_finish(_p(proj), ld, col0, rank, rot_dim, rot_dims, _p(w_norm), eps, _p(cs), half,
+                                                  float(mag), _p(kv.k), _p(kv.table), kv.table.shape[1], _p(ctx.token_seq),
+                                                  _p(ctx.positions), _p(ctx.slots), _p(rows), n, self._stream()))
+        return rows
+
+    def headwise(self, x, x_col: int, n_heads: int, head_stride: int, w, tail: int = 0, rot_dims: int = 0, cs=None,
+                 mag: float = 1.0, out_f32: bool = False) -> torch.Tensor:
+        """A matrix per head: ``out[t, h, :O] = x[t, x_col + h * head_stride : ... + I] . w[h]`` with ``w [H, I, O]``;
+        ``tail`` more columns of ``x`` behind a head's ``I`` are copied behind its outputs, the first ``rot_dims`` of them
+        turned.  ``x`` 32-bit ``[N, ld]``; returns ``[N, H, O + tail]`` (32-bit or the storage dtype)."""
+        self._need(x, torch.float32, "headwise input")
+        self._need(w, self.dtype, "headwise matrices")
+        n, ld = x.shape
+        H, I, O = w.shape
+        if H != n_heads or x_col + (H - 1) * head_stride + I + tail > ld:
+            raise KernelError(f"headwise: {H} heads of {I}+{tail} columns, stride {head_stride}, from column {x_col} of {ld}")
+        out = torch.empty((n, H, O + tail), dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+        half = 0 if cs is None else cs.shape[1]
+        self._check(self.lib.idm_headwise(x.data_ptr() + 4 * x_col, ld, head_stride, I, _p(w), O, _p(out), 1 if out_f32 else 0,
+                                          H * (O + tail), O + tail, tail, rot_dims, _p(cs), half, float(mag), n, H,
+                                          self._stream()))
+        return out
+
+    def latent_attention(self, qa, kv, ctx, rank: int, scale: float, sink=None) -> torch.Tensor:
+        """Causal attention of the step's queries ``qa [N, H, D]`` (32-bit, in the latent's space) over the cached rows
+        ``[c | r]`` of ``D`` numbers; returns the context ``[N, H * rank]`` in 32-bit: the weighted sums of ``c``.
+        Steps of few tokens cut the keys into runs of 256 positions, a block each, that meet in scratch."""
+        self._need(qa, torch.float32, "latent queries")
+        n, H, D = qa.shape
+        if tuple(kv.k.shape[1:]) != (1, self.page, D):
+            raise KernelError(f"cache entry {tuple(kv.k.shape)} does not fit rows of {D}")
+        if sink is not None:
+            self._need(sink, torch.float32, "sink")
+            if sink.numel() != H:
+                raise KernelError(f"{sink.numel()} sinks for {H} heads")
+        out = torch.empty((n, H * rank), dtype=torch.float32, device=self.device)
+        run_keys, n_runs, part = 256, 1, None
+        if n * (-(-H // 8)) < 2 * self.sm_count:
+            n_runs = max(1, -(-ctx.max_kv_len // run_keys))
+        if n_runs > 1:
+            part = self.scratch("latent_attention", n * H * n_runs * (rank + 2))
+        else:
+            run_keys = 1 << 30
+        self._check(self.lib.idm_latent_attention(_p(qa), _p(kv.k), _p(kv.table), kv.table.shape[1], _p(ctx.token_seq),
+                                                  _p(ctx.positions), _p(ctx.slots), _p(sink), _p(out), _p(part), n, H, rank,
+                                                  D, scale, run_keys, n_runs, self._stream()), 2 if n_runs > 1 else 1)
+        return out
+
+    # ---- experts chosen per token -------------------------------------------------------------------
+    def experts_from_table(self, tokens, table) -> torch.Tensor:
+        """``table[tokens]``: the experts ``[N, top]`` of the step's tokens from a table by token id."""
+        self._need(tokens, torch.int32, "tokens")
+        self._need(table, torch.int32, "expert table")
+        n, top = tokens.numel(), table.shape[1]
+        choice = torch.empty((n, top), dtype=torch.int32, device=self.device)
+        self._check(self.lib.idm_experts_from_table(_p(tokens), _p(table), top, _p(choice), n, self._stream()))
+        return choice
+
+    def experts_few(self, x, choice, gate, up, down, h, act: int, weight: float) -> None:
+        """``h[t] += weight * sum_k down[e] (act(gate[e] x_t) * up[e] x_t)``, ``e = choice[t, k]``: every (token, choice)
+        streams its expert's matrices (steps of few tokens)."""
+        self._need(x, self.dtype, "experts input")
+        self._need(h, torch.float32, "residual stream")
+        n, width = x.shape
+        E, ff, _ = gate.shape
+        top = choice.shape[1]
+        a = torch.empty((n, top, ff), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_experts_few(_p(x), _p(choice), _p(gate), _p(up), _p(down), _p(a), _p(h), n, width, ff, top, E,
+                                             act, float(weight), self._stream()), 2)
+
+    def rows_gather(self, x, src) -> torch.Tensor:
+        self._need(x, self.dtype, "rows")
+        self._need(src, torch.int32, "row numbers")
+        out = torch.empty((src.numel(), x.shape[1]), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_rows_gather(_p(x), _p(src), _p(out), src.numel(), x.shape[1], self._stream()))
+        return out
+
+    def experts_combine(self, z, place, h, weight: float) -> None:
+        """``h[t] += weight * sum_k z[place[t, k]]`` in ascending k (``place`` < 0: nothing)."""
+        self._need(z, torch.float32, "experts output")
+        self._need(place, torch.int32, "places")
+        n, width = h.shape
+        self._check(self.lib.idm_experts_combine(_p(z), _p(place), _p(h), n, width, place.shape[1], float(weight), self._stream()))
 
     def sample(self, logits: torch.Tensor, temperature: float, keys: Optional[torch.Tensor]) -> torch.Tensor:
         self._need(logits, torch.float32, "logits")

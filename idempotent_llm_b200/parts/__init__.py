@@ -2,16 +2,19 @@
 
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, FeedForward, Mixer, Norm,
                    NormedDelta, Part, PositionEncoding, Runtime)
-from .norm import RMSNorm
+from .norm import DyT, RMSNorm
 from .rotary import Rotary
 from .attention import GQAAttention
-from .mlp import GatedMLP
+from .mlp import DenseMLP, GatedMLP
 from .block import PreNormBlock
 from .sink_attention import SinkAttention
 from .ssd import SSDMixer
 from .parallel import ParallelMixer
 from .sandwich import SandwichBlock, TokenSide
+from .latent_attention import LatentAttention
+from .experts import TableExperts
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "FeedForward", "Mixer",
            "Norm", "NormedDelta", "Part", "PositionEncoding", "Runtime", "RMSNorm", "Rotary", "GQAAttention",
-           "GatedMLP", "PreNormBlock", "SinkAttention", "SSDMixer", "ParallelMixer", "SandwichBlock", "TokenSide"]
+           "GatedMLP", "PreNormBlock", "SinkAttention", "SSDMixer", "ParallelMixer", "SandwichBlock", "TokenSide",
+           "DyT", "DenseMLP", "LatentAttention", "TableExperts"]

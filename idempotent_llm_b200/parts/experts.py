@@ -1,0 +1,104 @@
+"""Feed-forward experts chosen by a table over token ids (a feed-forward).
+
+    out_t = (1 / top) * sum_k  down_e (act(gate_e x_t) * up_e x_t),   e = table[token_t, k]
+
+There is no learned router: which experts a token uses depends on its id alone, so the host knows a step's
+grouping wherever it holds the step's token ids.  Steps of many tokens use that: rows are gathered in the order of
+their experts, every expert with rows runs the gated feed-forward's two matrix products on its slice, and the
+outputs are added back in the order of a token's choices.  Steps of few tokens (and steps whose tokens exist on the
+device only: captured single-token steps) look the experts up on the device, and every (token, choice) streams its
+expert's matrices.  Both add into the 32-bit stream; they differ in the order of their sums, not in what is summed.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..weights.loader import TensorDecl
+from .base import FEED_FORWARDS, FeedForward
+from .mlp import ACTIVATIONS
+
+# steps with at least this many (token, choice) pairs group their rows by expert (where the host has the tokens)
+GROUP_FROM = 256
+
+
+@FEED_FORWARDS.register("table_experts")
+class TableExperts(FeedForward):
+    accepts_residual = True
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        s, nm = spec, spec.names
+        d = [TensorDecl(prefix + s.table, (s.vocab_size, s.top), init="choices", integer=True, high=s.n_experts)]
+        for e in range(s.n_experts):
+            p = prefix + s.expert.format(e)
+            d += [TensorDecl(p + nm.gate, (s.intermediate, s.hidden)), TensorDecl(p + nm.up, (s.intermediate, s.hidden)),
+                  TensorDecl(p + nm.down, (s.hidden, s.intermediate))]
+        return d
+
+    def __init__(self, spec, weights, prefix, rt):
+        s, nm = spec, spec.names
+        if s.activation not in ACTIVATIONS:
+            raise ValueError(f"activation {s.activation!r} is not built; known: {sorted(ACTIVATIONS)}")
+        self.spec, self.rt, self.act = spec, rt, ACTIVATIONS[s.activation]
+
+        def stack(name):
+            return torch.stack([weights[prefix + s.expert.format(e) + name].to(rt.dtype) for e in range(s.n_experts)]).contiguous()
+        self.gate, self.up, self.down = stack(nm.gate), stack(nm.up), stack(nm.down)     # [E, ff, W], [E, ff, W], [E, W, ff]
+        self.table = weights[prefix + s.table].to(torch.int32).contiguous()
+        self.table_host = self.table.cpu().numpy()
+        bad = (self.table_host < 0) | (self.table_host >= s.n_experts)
+        if bad.any():
+            raise ValueError(f"{prefix + s.table}: entries outside the {s.n_experts} experts")
+        K = rt.kernels
+        aligned = not (rt.dtype == torch.bfloat16 and (s.hidden % 8 or s.intermediate % 8))
+        self.fused = bool(getattr(K, "fused", False)) and aligned
+        self.can_group = aligned
+        # for the grouped path: gate and up of an expert as one matrix, in the layout its product's epilogue reads
+        self._gate_up = None
+
+    def _gate_up_of(self, e: int):
+        if self._gate_up is None:
+            K = self.rt.kernels
+            self._gate_up = [K.tile_gate_up(self.gate[i], self.up[i]) if self.fused
+                             else torch.cat([self.gate[i], self.up[i]], dim=0).contiguous() for i in range(self.spec.n_experts)]
+        return self._gate_up[e]
+
+    def forward(self, x, ctx, residual=None):
+        """Adds into ``residual`` and returns None (or returns the delta ``[1, N, hidden]``)."""
+        s, K = self.spec, self.rt.kernels
+        n = x.shape[0]
+        h = residual if residual is not None else torch.zeros((n, s.hidden), dtype=torch.float32, device=x.device)
+        toks = getattr(ctx, "host_tokens", None)
+        if toks is not None and self.can_group and n * s.top >= GROUP_FROM:
+            self._grouped(x, np.concatenate([np.asarray(t, dtype=np.int64) for t in toks]), h)
+        else:
+            choice = K.experts_from_table(ctx.tokens, self.table)
+            K.experts_few(x, choice, self.gate, self.up, self.down, h, self.act, 1.0 / s.top)
+        return None if residual is not None else h.unsqueeze(0)
+
+    def _grouped(self, x, tokens, h):
+        s, K = self.spec, self.rt.kernels
+        n, top = tokens.shape[0], s.top
+        choice = self.table_host[tokens].reshape(-1)                       # [n * top]: expert of (token, k)
+        order = np.argsort(choice, kind="stable")                          # grouped rows -> (token, k)
+        counts = np.bincount(choice, minlength=s.n_experts)
+        place = np.empty(n * top, dtype=np.int32)
+        place[order] = np.arange(n * top, dtype=np.int32)                  # (token, k) -> grouped row
+        both = torch.from_numpy(np.concatenate([(order // top).astype(np.int32), place])).to(x.device, non_blocking=True)
+        xg = K.rows_gather(x, both[:n * top])
+        z = torch.empty((n * top, s.hidden), dtype=torch.float32, device=x.device)
+        at = 0
+        for e in range(s.n_experts):
+            c = int(counts[e])
+            if not c:
+                continue
+            xe = xg[at:at + c]
+            if self.fused:
+                y = K.gemm_gated(xe, self._gate_up_of(e), s.intermediate, self.act)
+            else:
+                y = K.gated_act(K.gemm_store(xe, self._gate_up_of(e)), self.act)
+            z[at:at + c] = K.gemm_store(y, self.down[e])
+            at += c
+        K.experts_combine(z, both[n * top:].view(n, top), h, 1.0 / top)

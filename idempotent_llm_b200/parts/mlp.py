@@ -70,3 +70,38 @@ class GatedMLP(FeedForward):
         gu = K.gemm(x, self.w_gate_up, **self.pad)          # [P, N, 2 * intermediate]
         y = K.swiglu(gu) if self.act == 0 else K.gated_act(gu[0], self.act)      # [N, intermediate]
         return K.gemm(y, self.w_down, **self.pad)           # [P, N, hidden]
+
+
+# the kernels' numbers of the activations of one argument (csrc/elementwise.cu: act_cast)
+UNARY_ACTIVATIONS = {"relu2": 2}
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without a gate; ``relu2`` is the square of relu.  The activation runs in 32-bit on the
+    up product's 32-bit output and is rounded a single time, to the down product's input."""
+
+    accepts_residual = True
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        nm = spec.names
+        return [TensorDecl(prefix + nm.up, (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + nm.down, (spec.hidden, spec.intermediate))]
+
+    def __init__(self, spec, weights, prefix, rt):
+        if spec.activation not in UNARY_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not built; known: {sorted(UNARY_ACTIVATIONS)}")
+        self.spec, self.rt, self.act = spec, rt, UNARY_ACTIVATIONS[spec.activation]
+        nm = spec.names
+        self.w_up = weights[prefix + nm.up].to(rt.dtype).contiguous()
+        self.w_down = weights[prefix + nm.down].to(rt.dtype).contiguous()
+        self.pad = {"pad": True} if rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8) else {}
+
+    def forward(self, x, ctx, residual=None):
+        K = self.rt.kernels
+        y = K.act_cast(K.gemm_store(x, self.w_up, **self.pad), self.act)
+        if residual is not None and getattr(K, "fused", False) and not self.pad:
+            K.gemm_residual(y, self.w_down, residual)
+            return None
+        return K.gemm(y, self.w_down, **self.pad)

@@ -1,4 +1,5 @@
-"""RMS norm: ``x / sqrt(mean(x^2) + eps) * weight``, all in 32-bit.
+"""Norms.  RMS norm: ``x / sqrt(mean(x^2) + eps) * weight``, all in 32-bit; and, at the end of the file, a norm
+without statistics (``DyT``: ``tanh(alpha x) * w + b``).
 
 The reference's float form is ``x / sqrt(mean(x^2))`` (tests/test_ops.py:198-199,
 scripts/attribute_error.py:48-51) with the weight folded into the consumer
@@ -37,3 +38,29 @@ class RMSNorm(Norm):
 
     def emit(self, prog, h, out, rows=False):
         prog.add_rmsnorm(h, self.weight, self.spec.eps, out, self.spec.size, rows=rows)
+
+
+@NORMS.register("dyt")
+class DyT(Norm):
+    """``tanh(alpha x) * w + b`` element by element in 32-bit: no mean, no variance, so a row's elements do not
+    depend on one another.  A pending delta is added into the stream in the same pass."""
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        name = prefix + spec.weight
+        return [TensorDecl(name, (spec.size,), init="one_plus_normal"),
+                TensorDecl(name + spec.bias_suffix, (spec.size,)),
+                TensorDecl(name + spec.alpha_suffix, (), init="half_plus_normal")]
+
+    def __init__(self, spec, weights, prefix, rt):
+        self.spec, self.rt = spec, rt
+        name = prefix + spec.weight
+        self.weight = weights[name].to(torch.float32).contiguous()
+        self.bias = weights[name + spec.bias_suffix].to(torch.float32).contiguous()
+        self.alpha = float(weights[name + spec.alpha_suffix].to(torch.float32).item())     # one number, read once at load
+
+    def forward(self, h, delta, ctx, rows=None):
+        if isinstance(delta, NormedDelta):
+            delta.add_into(h, self.rt.kernels)
+            delta = None
+        return self.rt.kernels.add_dyt(h, delta, self.weight, self.bias, self.alpha, rows=rows)

@@ -17,6 +17,12 @@ import torch
 from .base import POSITIONS, PositionEncoding
 
 
+def magnitude(spec) -> float:
+    """What cos and sin are multiplied with: ``0.1 ln(factor) + 1`` under a ``RampScaling``, else 1."""
+    sc = getattr(spec, "scaling", None)
+    return 0.1 * math.log(sc.factor) + 1.0 if sc is not None and hasattr(sc, "fast") else 1.0
+
+
 def frequencies(spec) -> torch.Tensor:
     """``theta ** (-2 j / dim)`` for ``j < dim / 2`` in 64-bit, then the spec's scaling by wavelength, if any
     (``WavelengthScaling``: short waves kept, long waves divided by the factor, a linear blend between)."""
@@ -25,6 +31,13 @@ def frequencies(spec) -> torch.Tensor:
     sc = getattr(spec, "scaling", None)
     if sc is None:
         return f
+    if hasattr(sc, "fast"):                 # RampScaling: slowed down along a ramp over j between two borders
+        def at(turns):
+            return spec.dim * math.log(sc.original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(spec.theta)))
+        lo = max(math.floor(at(sc.fast)), 0)
+        hi = min(math.ceil(at(sc.slow)), spec.dim - 1)
+        ramp = torch.clamp((j - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / sc.factor * ramp + f * (1.0 - ramp)
     wave = 2.0 * math.pi / f
     s = (sc.original / wave - sc.low) / (sc.high - sc.low)
     blend = (1.0 - s) * f / sc.factor + s * f
@@ -39,8 +52,9 @@ class Rotary(PositionEncoding):
         self.spec = spec
         self.rt = rt
         self.inv_freq = frequencies(spec).to(rt.device)
+        self.magnitude = magnitude(spec)        # applied by the mixer's kernels (the table holds plain cos and sin)
         sc = getattr(spec, "scaling", None)
-        self._key = ("rotary", float(spec.theta), spec.dim, None if sc is None else (sc.factor, sc.low, sc.high, sc.original))
+        self._key = ("rotary", float(spec.theta), spec.dim, None if sc is None else tuple(sorted(vars(sc).items())))
 
     def emit(self, prog):
         """The table's two buffers in a step program (made once a step, like ``tables``)."""

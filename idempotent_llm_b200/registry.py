@@ -75,6 +75,8 @@ def _register_builtin() -> None:
     register_architecture(ARCHITECTURE, Qwen3Config)
     from .config.lunulix import ARCHITECTURE as LUNULIX, LunulixConfig
     register_architecture(LUNULIX, LunulixConfig)
+    from .config.panodra import ARCHITECTURE as PANODRA, PanodraConfig
+    register_architecture(PANODRA, PanodraConfig)
 
 
 _register_builtin()

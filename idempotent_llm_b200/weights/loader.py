@@ -28,12 +28,16 @@ from .safetensors_io import SafetensorsDir
 class TensorDecl:
     """A tensor a part needs: checkpoint name, shape, and how random init draws it
     (``normal``: N(0, std); ``one_plus_normal``: 1 + N(0, std), for norm weights; ``filter`` and
-    ``unit_normal``: N(0, 0.5), for a short filter's taps and per-head constants)."""
+    ``unit_normal``: N(0, 0.5), for a short filter's taps and per-head constants; ``half_plus_normal``: 0.5 + N(0, 0.1);
+    ``choices``: an integer table whose rows hold distinct numbers below ``high``).  ``integer``: the tensor is a
+    table of integers (kept as int32), not floating point."""
 
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"
     optional: bool = False   # present-or-absent both fine (an lm_head beside tied embeddings)
+    integer: bool = False
+    high: int = 0
 
 
 class WeightError(ValueError):
@@ -74,7 +78,7 @@ def check_declared(where: str, decls: Sequence[TensorDecl], have: Dict[str, Tupl
             dt, shape = have[n]
             if tuple(shape) != tuple(d.shape):
                 wrong_shape.append((n, tuple(shape), tuple(d.shape)))
-            if not isinstance(dt, torch.dtype) or not dt.is_floating_point:
+            if not isinstance(dt, torch.dtype) or dt.is_floating_point == d.integer or dt == torch.bool:
                 wrong_dtype.append((n, dt))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_dtype)

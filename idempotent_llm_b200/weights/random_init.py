@@ -26,6 +26,9 @@ def _tensor_seed(seed: int, name: str) -> int:
 def draw(decl: TensorDecl, seed: int, std: float, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, decl.name))
+    if decl.init == "choices":          # every row: distinct integers below `high`, in random order
+        rows, top = decl.shape
+        return torch.rand((rows, decl.high), generator=g, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
     t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     if decl.init in ("filter", "unit_normal"):
         t = t * 0.5             # taps of a short filter, per-head constants: of order one whatever `std` is
@@ -33,6 +36,8 @@ def draw(decl: TensorDecl, seed: int, std: float, dtype: torch.dtype, device="cp
         t = t * std
     if decl.init == "one_plus_normal":
         t = t + 1.0
+    elif decl.init == "half_plus_normal":
+        t = t / max(std, 1e-30) * 0.1 + 0.5
     elif decl.init not in ("normal", "filter", "unit_normal"):
         raise ValueError(f"unknown init {decl.init!r} for {decl.name}")
     return t.to(dtype)
