@@ -4,7 +4,7 @@
 //
 //     s = (qn . Uk_h c_j + qr . r_j) * scale = ((Uk_h^T qn) . c_j + qr . r_j) * scale
 //
-// so a step's queries are first carried into the latent's space (`latent_q_kernel`: qa = [Uk_h^T qn | turn(qr)]),
+// so a step's queries are first carried into the latent's space (`headwise_kernel`: qa = [Uk_h^T qn | turn(qr)]),
 // every head then reads the same cached rows (`latent_attention_kernel`: scores against [c | r], the context
 // as a weighted sum of c), and the head's value map is applied once to the context (`headwise_kernel`).  The
 // cache is read once per token and step whatever the number of heads.  All arithmetic here is 32-bit; the cache
@@ -365,5 +365,70 @@ extern "C" int idm_latent_attention(const float* qa, const void* pool, const int
                    positions, n_tokens, H, R, run_keys, n_runs);
         IDM_LAUNCH_CHECK("latent_fold");
     }
+    return 0;
+}
+
+// ------------------------------------------------------------------ whole prompts: keys and values per head
+// A step that brings whole prompts (every sequence from its first token) has more queries than heads' worth of
+// latent space pays for: there the keys and values are made per head from the step's rows once, k_h = [Uk_h c | r]
+// and v_h = Uv_h c, and the step runs the attention kernel for heads with keys and values of their own.  This
+// kernel lays its operands out: q [N, H, hd] = [qn | turn(qr) | 0], and pages of their own [pages, H, PAGE, hd]
+// for k and v (0 behind a head's own dims), addressed through a block table of the step's own.
+// proj: the joint projection (a head's query at column h * (dn + dr)); up: [N, H * dn + H * dv] = the rows' c times
+// [Uk ; Uv]; rows: the step's packed [c | r] rows in the storage type.  One block per token.
+__global__ void __launch_bounds__(256) latent_expand_pack_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ up,
+                                                                 const T* __restrict__ rows, int H, int dn, int dr, int dv, int R,
+                                                                 int rot_dims, const float2* __restrict__ cs, int half, float mag,
+                                                                 int hd, T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
+                                                                 const int* __restrict__ table, int table_stride,
+                                                                 const int* __restrict__ token_seq, const int* __restrict__ positions,
+                                                                 const int* __restrict__ slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t], slot = slots[token_seq[t]];
+    const int page = table[(size_t)slot * table_stride + pos / IDM_PAGE];
+    const float* pq = proj + (size_t)t * ld;
+    const float* pu = up + (size_t)t * (size_t)(H * dn + H * dv);
+    const T* r = rows + (size_t)t * (R + dr) + R;
+    for (int e = threadIdx.x; e < H * hd; e += blockDim.x) {
+        const int h = e / hd, d = e % hd;
+        float qv = 0.f;
+        T kk, vv;
+        from_f32(kk, 0.f); from_f32(vv, 0.f);
+        if (d < dn) {
+            qv = pq[h * (dn + dr) + d];
+            from_f32(kk, pu[h * dn + d]);
+        } else if (d < dn + dr) {
+            const int j = d - dn;
+            const float* qr = pq + h * (dn + dr) + dn;
+            qv = qr[j];
+            if ((j | 1) < rot_dims) {                       // the pair (j & ~1, j | 1) is turned
+                const float2 a = cs[(size_t)t * half + (j >> 1)];
+                const float co = a.x * mag, si = a.y * mag;
+                qv = (j & 1) ? qr[j] * co + qr[j - 1] * si : qr[j] * co - qr[j + 1] * si;
+            }
+            kk = r[j];
+        }
+        if (d < dv) from_f32(vv, pu[H * dn + h * dv + d]);
+        from_f32(q[((size_t)t * H + h) * hd + d], qv);
+        const size_t at = (((size_t)page * H + h) * IDM_PAGE + pos % IDM_PAGE) * hd + d;
+        k[at] = kk;
+        v[at] = vv;
+    }
+}
+
+extern "C" int idm_latent_expand_pack(const float* proj, int ld, const float* up, const void* rows, int H, int dn, int dr,
+                                      int dv, int R, int rot_dims, const float* cs, int half, float mag, int hd, void* q,
+                                      void* k, void* v, const int* table, int table_stride, const int* token_seq,
+                                      const int* positions, const int* slots, int n_tokens, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && dv > 0 && dn + dr <= hd && dv <= hd, "latent_expand_pack: heads of %d + %d and %d in %d",
+                dn, dr, dv, hd);
+    IDM_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || (cs != nullptr && half >= rot_dims / 2)),
+                "latent_expand_pack: %d turned dims of %d with a table of %d angles", rot_dims, dr, half);
+    idm_launch(latent_expand_pack_kernel, dim3(n_tokens), dim3(256), 0, stream, proj, ld, up, (const T*)rows, H, dn, dr, dv, R, rot_dims,
+               (const float2*)cs, half, mag, hd, (T*)q, (T*)k, (T*)v, table, table_stride, token_seq, positions, slots);
+    IDM_LAUNCH_CHECK("latent_expand_pack");
     return 0;
 }

@@ -96,6 +96,7 @@ SIGNATURES = {
     "idm_headwise": (c_int, "pqiipipiqiiipifiip"),
     "idm_latent_attention_max_rank": (c_int, ""),
     "idm_latent_attention": (c_int, "pppippppppiiiifiip"),
+    "idm_latent_expand_pack": (c_int, "pippiiiiiipifippppipppip"),
     "idm_experts_from_table": (c_int, "ppipip"),
     "idm_experts_few": (c_int, "pppppppiiiiiifp"),
     "idm_rows_gather": (c_int, "pppiip"),
@@ -905,6 +906,19 @@ class Kernels:
                                                   _p(ctx.positions), _p(ctx.slots), _p(sink), _p(out), _p(part), n, H, rank,
                                                   D, scale, run_keys, n_runs, self._stream()), 2 if n_runs > 1 else 1)
         return out
+
+    def latent_expand_pack(self, proj, up, rows, H, dn, dr, dv, R, rot_dims, cs, mag, hd, table, n_pages, ctx):
+        """The operands of the per-head attention kernel for a step of whole prompts: ``q [N, H, hd]`` and pages of the
+        step's own for k and v ``[n_pages, H, PAGE, hd]``, zero behind a head's own dims (see csrc/latent.cu)."""
+        n = proj.shape[0]
+        q = torch.empty((n, H, hd), dtype=self.dtype, device=self.device)
+        k = torch.empty((n_pages, H, self.page, hd), dtype=self.dtype, device=self.device)
+        v = torch.empty((n_pages, H, self.page, hd), dtype=self.dtype, device=self.device)
+        half = 0 if cs is None else cs.shape[1]
+        self._check(self.lib.idm_latent_expand_pack(_p(proj), proj.shape[1], _p(up), _p(rows), H, dn, dr, dv, R, rot_dims, _p(cs),
+                                                    half, float(mag), hd, _p(q), _p(k), _p(v), _p(table), table.shape[1],
+                                                    _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), n, self._stream()))
+        return q, k, v
 
     # ---- experts chosen per token -------------------------------------------------------------------
     def experts_from_table(self, tokens, table) -> torch.Tensor:

@@ -14,12 +14,18 @@ A token keeps the row ``[c_t | r_t]`` and nothing per head.  The kernels work in
 becomes ``[Uk_i^T qn_i | qr_i]``, every head scores the same cached rows, the context is a weighted sum of ``c``, and
 ``Uv_i`` is applied once to that sum: the same sums in another order.  Scores, softmax, the latent's norm and the
 rotation are 32-bit; matrices, the cached rows and the products' inputs are in the storage dtype.
+
+A step of whole prompts (every sequence from its first token) has many queries per cached row; in bfloat16, with
+heads that fit the tensor-core attention kernel, it makes every head's keys and values from the step's rows with one
+matrix product and runs that kernel over pages of the step's own (``_whole_prompts``).  The cache receives the same
+rows either way, so later single tokens read what the prompt left.
 """
 
 from __future__ import annotations
 
 import torch
 
+from ..cache.sequence_cache import KVView
 from ..cache.spec import CacheNeed
 from ..weights.loader import TensorDecl
 from .base import MIXERS, POSITIONS, Mixer
@@ -75,6 +81,54 @@ class LatentAttention(Mixer):
         self.sink = weights[prefix + nm.sink].to(torch.float32).contiguous() if s.sink else None
         self.w_o = weights[prefix + nm.o].to(rt.dtype).contiguous()
         self.pad = {"pad": True} if rt.dtype == torch.bfloat16 and (s.hidden % 8 or (H * dv) % 8) else {}
+        # whole prompts on the tensor cores: heads padded to a head size that kernel has
+        self.tc_hd = 0
+        K = rt.kernels
+        if (rt.dtype == torch.bfloat16 and getattr(K, "fused", False) and getattr(K, "attention_impl", "") == "tcgen05"
+                and not self.pad and (R + s.rot_dim) % 8 == 0):
+            need = max(dn + s.rot_dim, dv)
+            self.tc_hd = 64 if need <= 64 else 128 if need <= 128 else 0
+        if self.tc_hd:
+            hd = self.tc_hd
+            up = torch.zeros((H * dn + H * dv, R + s.rot_dim), dtype=rt.dtype, device=rt.device)
+            up[:H * dn, :R] = weights[prefix + nm.up_k].to(rt.dtype)
+            up[H * dn:, :R] = weights[prefix + nm.up_v].to(rt.dtype)
+            self.w_up = up.contiguous()                      # [Uk ; Uv] over a cached row (zero over its rotated part)
+            wo = torch.zeros((s.hidden, H, hd), dtype=rt.dtype, device=rt.device)
+            wo[:, :, :dv] = self.w_o.view(s.hidden, H, dv)
+            self.w_o_padded = wo.view(s.hidden, H * hd).contiguous()
+
+    # steps of whole prompts take the per-head kernel from this many tokens in the longest prompt on
+    WHOLE_FROM = 32
+
+    def _step_pages(self, ctx):
+        """A block table of the step's own: sequence i's pages one after another (made once a step)."""
+        made = ctx.memo.get("latent_step_pages")
+        if made is None:
+            page = self.rt.kernels.page
+            table = torch.zeros((max(ctx.host_slots) + 1, max(-(-n // page) for n in ctx.host_q_lens)), dtype=torch.int32)
+            at = 0
+            for slot, n in zip(ctx.host_slots, ctx.host_q_lens):
+                pages = -(-n // page)
+                table[slot, :pages] = torch.arange(at, at + pages, dtype=torch.int32)
+                at += pages
+            made = ctx.memo["latent_step_pages"] = (table.to(self.rt.device), at)
+        return made
+
+    def _whole_prompts(self, proj, cs, ctx, kv, residual):
+        s, K, hd = self.spec, self.rt.kernels, self.tc_hd
+        rows = K.latent_kv_finish(proj, self.q_cols, s.kv_rank, s.rot_dim, self.rot_dims, self.down_norm, s.eps, cs,
+                                  self.magnitude, kv, ctx, keep_rows=True)
+        up = K.gemm_store(rows, self.w_up)                                  # 32-bit [N, H * plain_dim + H * value_dim]
+        table, n_pages = self._step_pages(ctx)
+        q, k, v = K.latent_expand_pack(proj, up, rows, s.n_heads, s.plain_dim, s.rot_dim, s.value_dim, s.kv_rank,
+                                       self.rot_dims, cs, self.magnitude, hd, table, n_pages, ctx)
+        own = KVView(k=k, v=v, table=table, ring=0, n_kv_heads=s.n_heads, head_dim=hd, window=None)
+        o = K.attention_tc(q, own, ctx, s.softmax_scale, sink=self.sink)    # [N, H * hd]
+        if residual is not None:
+            K.gemm_residual(o, self.w_o_padded, residual)
+            return None
+        return K.gemm(o, self.w_o_padded)
 
     def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None):
         """Returns the delta ``[1, N, hidden]``, or None after adding it into ``residual`` in place."""
@@ -83,6 +137,8 @@ class LatentAttention(Mixer):
         s, K = self.spec, self.rt.kernels
         cs = self.position.tables(ctx) if self.position is not None else None
         proj = K.gemm_store(x, self.w_in, **self.pad)                       # 32-bit [N, q columns + rank + rot_dim]
+        if self.tc_hd and not ctx.single_token and ctx.max_q_len >= self.WHOLE_FROM and not any(ctx.host_starts):
+            return self._whole_prompts(proj, cs, ctx, kv, residual)
         K.latent_kv_finish(proj, self.q_cols, s.kv_rank, s.rot_dim, self.rot_dims, self.down_norm, s.eps, cs,
                            self.magnitude, kv, ctx)
         # queries into the latent's space, their rotated part turned: [N, H, rank + rot_dim], 32-bit

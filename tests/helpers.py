@@ -194,3 +194,94 @@ def read_lunulix(model_dir: str):
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
     return cfg, load_file(os.path.join(model_dir, "model.safetensors"))
+
+
+# ------------------------------------------------------------------------------------- Panodra
+def panodra_layer(sink=False, heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40, scale=0.2, rot_base=3e4, scaling=None,
+                  mlp="dense", ff=72, experts=5, top=3):
+    """One layer of a Panodra config.json; every size and constant is an argument.  ``scaling``: (factor, original,
+    fast, slow) or None; ``mlp``: "dense", "moe" or None."""
+    rot = dict(base=rot_base, dims=rot_dim)
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    m = None
+    if mlp == "dense":
+        m = dict(kind="dense", ff=ff)
+    elif mlp == "moe":
+        m = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+    return dict(type="latent_attention" if sink else "latent_attention_2",
+                mixer=dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, scale=scale, rot=rot), mlp=m)
+
+
+def panodra_config(layers, vocab=97, width=64, eps=1e-5, loop=None, logit_scale=0.7, softcap=12.0):
+    d = dict(architecture="Panodra", vocab=vocab, width=width, norm=dict(eps=eps), layers=list(layers))
+    if loop:
+        d["loop"] = dict(zip(("start", "stop", "times"), loop))
+    if logit_scale is not None:
+        d["logit_scale"] = logit_scale
+    if softcap is not None:
+        d["logit_softcap"] = softcap
+    return d
+
+
+# Small Panodra models that differ from one another in every size and option.
+PANODRA = {
+    # three unlike layers, the last two run three times: no sink / dense, sink + scaled frequencies / experts 3 of 5,
+    # sink / no feed-forward
+    "A": lambda: panodra_config([
+        panodra_layer(),
+        panodra_layer(sink=True, heads=2, dim=8, rot_dim=16, vdim=8, kv_rank=24, scale=0.35, rot_base=1e4,
+                      scaling=(8.0, 64, 8.0, 1.0), mlp="moe", ff=24, experts=5, top=3),
+        panodra_layer(sink=True, heads=4, dim=24, rot_dim=8, vdim=16, kv_rank=32, scale=0.15, mlp=None)], loop=(1, 3, 3)),
+    # values of 1 and absent keys: one head, one expert of which a token uses one, no loop, no constant, no cap
+    "B": lambda: panodra_config([panodra_layer(heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=16, mlp="moe", ff=16, experts=1, top=1)],
+                                vocab=50, width=24, loop=None, logit_scale=None, softcap=None),
+    # widths that are no multiple of 8 (bfloat16 rows off the 16-byte borders), a loop of one layer over the first
+    "C": lambda: panodra_config([
+        panodra_layer(sink=True, heads=3, dim=12, rot_dim=6, vdim=10, kv_rank=12, scale=0.3, ff=28),
+        panodra_layer(heads=2, dim=6, rot_dim=4, vdim=6, kv_rank=10, scale=0.4, mlp="moe", ff=12, experts=3, top=2)],
+        vocab=33, width=20, loop=(0, 1, 2), logit_scale=1.3, softcap=5.0),
+    # head sizes the tensor-core attention takes whole prompts at (64 and 128 with the heads padded), experts that
+    # run grouped by expert from 128 tokens on
+    "T": lambda: panodra_config([
+        panodra_layer(heads=4, dim=32, rot_dim=32, vdim=64, kv_rank=64, scale=0.12, ff=160),
+        panodra_layer(sink=True, heads=3, dim=64, rot_dim=32, vdim=80, kv_rank=96, scale=0.1, scaling=(4.0, 128, 16.0, 1.0),
+                      mlp="moe", ff=64, experts=4, top=2)], vocab=211, width=128, loop=(0, 2, 2)),
+}
+
+
+def panodra_random_config(seed: int) -> dict:
+    """A Panodra configuration drawn from sizes a model of the design may have."""
+    import random
+    r = random.Random(seed)
+
+    def layer():
+        rot_dim = r.choice([8, 16, 32, 64]); dim = r.choice([16, 32, 64, 96, 128])
+        return panodra_layer(sink=r.random() < 0.5, heads=r.choice([1, 2, 4, 6, 8]), dim=dim, rot_dim=rot_dim,
+                             vdim=r.choice([16, 32, 64, 80, 128]), kv_rank=r.choice([32, 64, 96, 128, 256]),
+                             scale=r.choice([(dim + rot_dim) ** -0.5, 0.1, 0.05]), rot_base=r.choice([1e4, 2.5e5, 1e6]),
+                             scaling=r.choice([None, (4.0, 1024, 32.0, 1.0), (16.0, 64, 4.0, 0.5), (2.0, 256, 8.0, 2.0)]),
+                             mlp=r.choice(["dense", "moe", "moe", None]), ff=r.choice([64, 96, 160]),
+                             experts=r.choice([2, 4, 9]), top=r.choice([1, 2]))
+    n = r.choice([1, 2, 3, 4])
+    a = r.randrange(n); b = r.randrange(a + 1, n + 1)
+    return panodra_config([layer() for _ in range(n)], vocab=r.choice([128, 500, 1000]), width=r.choice([64, 96, 128, 256]),
+                          eps=r.choice([1e-5, 1e-6]), loop=r.choice([None, (a, b, r.choice([1, 2, 3]))]),
+                          logit_scale=r.choice([None, 0.5, 2.0]), softcap=r.choice([None, 30.0, 8.0]))
+
+
+def make_panodra_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.2, edit=None) -> str:
+    """A Panodra model folder with seeded random weights; ``edit(name, tensor) -> tensor`` may change them."""
+    from idempotent_llm_b200.config import PanodraConfig
+    from idempotent_llm_b200.weights import write_random_model, write_safetensors, SafetensorsFile
+    write_random_model(PanodraConfig.from_dict(cfg), out_dir, seed=seed, dtype=dtype, std=std)
+    if edit is not None:
+        path = os.path.join(out_dir, "model.safetensors")
+        f = SafetensorsFile(path)
+        tensors = [(n, edit(n, f.get(n).clone())) for n in f.names()]
+        del f
+        write_safetensors(path, tensors)
+    return out_dir
+
+
+read_model_dir = read_lunulix        # (config dict, tensors by name) of any model folder
