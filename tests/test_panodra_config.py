@@ -99,7 +99,7 @@ def test_a_random_folder_is_loaded_by_name(tmp_path):
     assert table.dtype == torch.int32 and int(table.min()) >= 0 and int(table.max()) < 5
     assert all(len(set(row)) == 3 for row in table.tolist())               # a row's experts differ
     assert w["l0.norm1.alpha"].shape == () and 0.0 < float(w["l0.norm1.alpha"]) < 1.0
-    # an integer table where a floating-point tensor is declared, and the other way round, is refused
+    # an integer table where a floating-point tensor is declared is refused
     from idempotent_llm_b200.weights import SafetensorsFile, WeightError, write_safetensors
     path = os.path.join(d, "model.safetensors")
     f = SafetensorsFile(path)
