@@ -161,7 +161,7 @@ def decode_point(lm, lens, steps: int, warmup: int, seed: int, repeats: int = 1,
     ms = statistics.median(times)
     sess.finish()
     mean_len = sum(l + warmup + repeats * steps / 2 for l in lens)
-    bytes_step = lm.model.weight_bytes() + kv_bytes_per_token(eng) * mean_len + 2 * batch * state_bytes_per_sequence(eng)
+    bytes_step = step_weight_bytes(lm, batch) + kv_bytes_per_token(eng) * mean_len + 2 * batch * state_bytes_per_sequence(eng)
     toks = sess.tokens()
     assert toks.shape == (total, batch) and int(toks.min()) >= 0 and int(toks.max()) < V
     for s in slots:
@@ -219,9 +219,45 @@ def lunulix_prefill_flops(cfg, lens) -> float:
     return total + 2 * W * cfg.vocab * len(lens)
 
 
+def panodra_prefill_flops(cfg, lens) -> float:
+    """The same count for a Panodra configuration, per layer run: the joint input projection, every head's keys and
+    values from the latent, the output projection, causal attention per head over keys of dim + rot_dim and values of
+    vdim, the feed-forward a token uses (dense: two matrices; experts: `top` times three), and the mixes that open
+    a pass."""
+    W, tokens, total = cfg.width, sum(lens), 0.0
+    spec = cfg.to_model_spec()
+    for e in spec.schedule:
+        L = cfg.layers[e.layer]
+        m = L.mixer
+        linear = W * (m.heads * (m.dim + m.rot_dim) + m.kv_rank + m.rot_dim) + m.kv_rank * m.heads * (m.dim + m.vdim) + m.heads * m.vdim * W
+        if L.mlp is not None:
+            linear += 2 * W * L.mlp.ff if L.mlp.kind == "dense" else 3 * W * L.mlp.ff * L.mlp.top
+        if e.mix_in:
+            linear += 2 * W * W
+        total += 2 * tokens * linear
+        total += sum(m.heads * 2 * (m.dim + m.rot_dim + m.vdim) * t * (t + 1) // 2 for t in lens)
+    return total + 2 * W * cfg.vocab * len(lens)
+
+
+def step_weight_bytes(lm, batch: int) -> float:
+    """Bytes of weights a single-token step of ``batch`` sequences reads: every matrix once, but of a layer's experts
+    only those the step's tokens use (expected number when every token draws its `top` of E alike)."""
+    total = float(lm.model.weight_bytes())
+    for b in lm.model.blocks:
+        ff = getattr(b, "feed_forward", None)
+        if ff is not None and hasattr(ff, "gate_up") and ff.gate_up.dim() == 3:
+            E, top = ff.spec.n_experts, ff.spec.top
+            used = E * (1.0 - (1.0 - top / E) ** batch)
+            per = sum(t[0].numel() * t.element_size() for t in (ff.gate_up, ff.down))
+            total -= (E - used) * per
+    return total
+
+
 def prefill_flops(cfg, lens) -> float:
     """Multiply-adds x 2 of a step that brings whole prompts of ``lens`` tokens: the layers' products, causal
     attention, and the head at each prompt's last position."""
+    if getattr(cfg, "architecture", "") == "Panodra":
+        return panodra_prefill_flops(cfg, lens)
     if hasattr(cfg, "layers") and not hasattr(cfg, "hidden_size"):
         return lunulix_prefill_flops(cfg, lens)
     H, L, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size
@@ -340,7 +376,7 @@ def kernel_times(lm, lens, seed: int):
     g = torch.Generator().manual_seed(seed)
     names = [n for n in dir(K) if not n.startswith("_") and callable(getattr(K, n)) and n not in
              ("scratch", "attention_tc_plan", "attention_tc_status", "gemm_status", "gemm_choices", "attention_tc_few_rows",
-              "tile_gate_up", "attention", "gemm", "wait_probe", "sample", "attention_tc_fits", "ssd_chunks")]
+              "tile_gate_up", "attention", "gemm", "wait_probe", "sample", "attention_tc_fits", "ssd_chunks", "latent_max_rank")]
     out, saved = {}, {n: getattr(K, n) for n in names}
     timing = [False]
 
@@ -388,7 +424,8 @@ def decode_kernel_times(lm, lens, seed: int):
     K = lm.model.rt.kernels
     names = ["embed", "embed_scaled", "add_rmsnorm", "post_pre_norm", "rope_table", "gemm_store", "gemm_residual", "gemm_swiglu",
              "gemm_gated", "gemm_qkv", "attention_tc", "attention_generic", "attention_sink", "conv_qkv_cache", "short_conv",
-             "ssd_scan", "ssd_group_norm", "token_gate", "gated_act", "attention_lse_gate"]
+             "ssd_scan", "ssd_group_norm", "token_gate", "gated_act", "attention_lse_gate", "add_dyt", "latent_kv_finish",
+             "headwise", "latent_attention", "experts_few", "act_cast", "concat_cast", "logit_cap"]
     names = [n for n in names if hasattr(K, n)]
     out, saved = {}, {n: getattr(K, n) for n in names}
     timing = [False]
@@ -424,8 +461,9 @@ def decode_kernel_times(lm, lens, seed: int):
 
 
 def design_comparison(args) -> int:
-    """``--design lunulix``: decode and prefill throughput of the Lunulix design beside Qwen3 at equal width, depth,
-    heads, feed-forward size and vocabulary (random weights), with where a step's time goes kernel by kernel."""
+    """``--design lunulix`` / ``--design panodra``: decode and prefill throughput of that design beside Qwen3 at equal
+    width, depth (layer runs), heads, feed-forward size and vocabulary (random weights), with where a step's time goes
+    kernel by kernel."""
     import torch
     import idempotent_llm_b200 as idm
     from idempotent_llm_b200.config.presets import preset
@@ -483,7 +521,7 @@ def main() -> int:
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median counts")
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the 32-bit check")
     ap.add_argument("--skip-sizes", action="store_true", help="leave out the points at 8B and 32B layer sizes")
-    ap.add_argument("--design", default="", choices=["", "lunulix"],
+    ap.add_argument("--design", default="", choices=["", "lunulix", "panodra"],
                     help="instead of the default workload: this design beside qwen3 at equal layer sizes")
     ap.add_argument("--design-sizes", default="0.6b,8b", help="layer sizes of --design (presets <design>-<size>)")
     args = ap.parse_args()

@@ -1,28 +1,10 @@
 // Feed-forward experts chosen per token: out[t] = weight * sum_k down_e (act(gate_e x_t) * up_e x_t), e = the
-// k-th expert of token t.  These kernels serve steps of few tokens (single tokens above all): every (token,
+// k-th expert of token t = table[token id of t, k] (a table of integers [vocabulary, top]).  These kernels serve steps of few tokens (single tokens above all): every (token,
 // choice) streams its expert's matrices once, a warp per output row, sums in 32-bit in a fixed order, so a
 // token's result does not depend on what else the step holds.  Steps of many tokens group their rows by expert
 // on the host and run one matrix product per expert instead; the kernels below then gather the rows
 // (rows_gather) and add the experts' outputs back in the order of a token's choices (experts_combine).
 #include "common.cuh"
-
-// the experts of the step's tokens from a table by token id: choice[t, k] = table[tokens[t], k]
-__global__ void __launch_bounds__(256) experts_from_table_kernel(const int* __restrict__ tokens, const int* __restrict__ table,
-                                                                 int top, int* __restrict__ choice, int n) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n * top) choice[i] = table[(size_t)tokens[i / top] * top + i % top];
-}
-
-extern "C" int idm_experts_from_table(const int* tokens, const int* table, int top, int* choice, int n_tokens,
-                                      cudaStream_t stream) {
-    if (n_tokens == 0) return 0;
-    IDM_REQUIRE(top > 0, "experts_from_table: top=%d", top);
-    idm_launch(experts_from_table_kernel, dim3((n_tokens * top + 255) / 256), dim3(256), 0, stream, tokens, table, top, choice, n_tokens);
-    IDM_LAUNCH_CHECK("experts_from_table");
-    return 0;
-}
 
 __device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int K, int lane, bool vec) {
     float s = 0.f;
@@ -39,32 +21,64 @@ __device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* _
     return warp_sum(s);
 }
 
-// a[t, k, f] = act(gate_e[f] . x_t) * (up_e[f] . x_t), 32-bit; gate, up: [E, ff, width]; a block has one
-// (token, choice) and 8 rows f per pass of its warps
-__global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ choice,
-                                                              const T* __restrict__ gate, const T* __restrict__ up,
+// two rows against two vectors at once: four 16-byte loads of a lane are in flight before the first is used
+__device__ __forceinline__ void row_dot2(const T* __restrict__ w0, const T* __restrict__ w1, const float* __restrict__ x0,
+                                         const float* __restrict__ x1, int K, int lane, bool vec, float& r0, float& r1) {
+    float s0 = 0.f, s1 = 0.f;
+    if (vec) {
+        constexpr int VN = Vec16<T>::N;
+        int d = lane * VN;
+        for (; d + 32 * VN < K; d += 64 * VN) {
+            Vec16<T> a0, a1, b0, b1;
+            a0.load(w0 + d); b0.load(w1 + d); a1.load(w0 + d + 32 * VN); b1.load(w1 + d + 32 * VN);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) { s0 = fmaf(x0[d + e], a0.get(e), s0); s1 = fmaf(x1[d + e], b0.get(e), s1); }
+#pragma unroll
+            for (int e = 0; e < VN; ++e) { s0 = fmaf(x0[d + 32 * VN + e], a1.get(e), s0); s1 = fmaf(x1[d + 32 * VN + e], b1.get(e), s1); }
+        }
+        for (; d < K; d += 32 * VN) {
+            Vec16<T> a0, b0;
+            a0.load(w0 + d); b0.load(w1 + d);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) { s0 = fmaf(x0[d + e], a0.get(e), s0); s1 = fmaf(x1[d + e], b0.get(e), s1); }
+        }
+    } else {
+        for (int d = lane; d < K; d += 32) { s0 = fmaf(x0[d], to_f32(w0[d]), s0); s1 = fmaf(x1[d], to_f32(w1[d]), s1); }
+    }
+    r0 = warp_sum(s0); r1 = warp_sum(s1);
+}
+
+// a[t, k, f] = act(gate_e[f] . x_t) * (up_e[f] . x_t), 32-bit.  Gate and up rows of an expert lie in one array:
+// row f of expert e starts at e * expert_stride + f * row_stride (gate) and up_off behind that (up), which serves both
+// "gate rows, then up rows" and "gate and up rows alternating" (the layout a gated product's epilogue reads).
+// A block has one (token, choice) and 8 rows f per pass of its warps.
+__global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens,
+                                                              const int* __restrict__ table, const T* __restrict__ gate_up, long long expert_stride,
+                                                              long long row_stride, long long up_off,
                                                               float* __restrict__ a, int width, int ff, int top, int n_experts,
                                                               int act) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float xs[];
     const int tk = blockIdx.x;
-    const int e = choice[tk];
     const int t = tk / top;
+    const int e = table[(size_t)tokens[t] * top + tk % top];       // the token's id names its experts
     for (int d = threadIdx.x; d < width; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * width + d]);
     __syncthreads();
     if (e < 0 || e >= n_experts) return;                     // (a table entry outside the experts: contributes nothing)
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec = (width * (int)sizeof(T)) % 16 == 0;
     for (int f = blockIdx.y * 8 + wib; f < ff; f += gridDim.y * 8) {
-        const size_t row = ((size_t)e * ff + f) * width;
-        const float g = row_dot(gate + row, xs, width, lane, vec), u = row_dot(up + row, xs, width, lane, vec);
+        const T* row = gate_up + (size_t)e * expert_stride + (size_t)f * row_stride;
+        float g, u;
+        row_dot2(row, row + up_off, xs, xs, width, lane, vec, g, u);
         if (lane == 0) a[(size_t)tk * ff + f] = gated_act(g, u, act);
     }
 }
 
 // h[t, w] += weight * sum_k down_e[w] . a[t, k];  down: [E, width, ff]; a block has one token, a warp an output row
-__global__ void __launch_bounds__(256) experts_down_kernel(const float* __restrict__ a, const int* __restrict__ choice,
+__global__ void __launch_bounds__(256) experts_down_kernel(const float* __restrict__ a, const int* __restrict__ tokens,
+                                                           const int* __restrict__ table,
                                                            const T* __restrict__ down, float* __restrict__ h, int width,
                                                            int ff, int top, int n_experts, float weight) {
     pdl_launch_dependents();
@@ -77,8 +91,22 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const float* __restri
     const bool vec = (ff * (int)sizeof(T)) % 16 == 0;
     for (int w = blockIdx.y * 8 + wib; w < width; w += gridDim.y * 8) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = choice[t * top + k];
+        int k = 0;
+        for (; k + 1 < top; k += 2) {                       // two choices' rows at once (their loads side by side)
+            const int e0 = table[(size_t)tokens[t] * top + k], e1 = table[(size_t)tokens[t] * top + k + 1];
+            const bool ok0 = e0 >= 0 && e0 < n_experts, ok1 = e1 >= 0 && e1 < n_experts;
+            if (ok0 && ok1) {
+                float r0, r1;
+                row_dot2(down + ((size_t)e0 * width + w) * ff, down + ((size_t)e1 * width + w) * ff, as + k * ff, as + (k + 1) * ff,
+                         ff, lane, vec, r0, r1);
+                s += r0; s += r1;
+            } else {
+                if (ok0) s += row_dot(down + ((size_t)e0 * width + w) * ff, as + k * ff, ff, lane, vec);
+                if (ok1) s += row_dot(down + ((size_t)e1 * width + w) * ff, as + (k + 1) * ff, ff, lane, vec);
+            }
+        }
+        for (; k < top; ++k) {
+            const int e = table[(size_t)tokens[t] * top + k];
             if (e < 0 || e >= n_experts) continue;
             s += row_dot(down + ((size_t)e * width + w) * ff, as + k * ff, ff, lane, vec);
         }
@@ -86,7 +114,8 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const float* __restri
     }
 }
 
-extern "C" int idm_experts_few(const void* x, const int* choice, const void* gate, const void* up, const void* down,
+extern "C" int idm_experts_few(const void* x, const int* tokens, const int* table, const void* gate_up, long long expert_stride,
+                               long long row_stride, long long up_off, const void* down,
                                float* a, float* h, int n_tokens, int width, int ff, int top, int n_experts, int act,
                                float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
@@ -100,10 +129,10 @@ extern "C" int idm_experts_few(const void* x, const int* choice, const void* gat
     // blocks along the rows: enough to fill the part for one token, fewer per token as tokens grow
     const int by1 = max(1, min((ff + 7) / 8, 592 / max(1, n_tokens * top)));
     const int by2 = max(1, min((width + 7) / 8, 592 / max(1, n_tokens)));
-    idm_launch(experts_gate_up_kernel, dim3(n_tokens * top, by1), dim3(256), s1, stream, (const T*)x, choice, (const T*)gate,
-               (const T*)up, a, width, ff, top, n_experts, act);
+    idm_launch(experts_gate_up_kernel, dim3(n_tokens * top, by1), dim3(256), s1, stream, (const T*)x, tokens, table, (const T*)gate_up,
+               expert_stride, row_stride, up_off, a, width, ff, top, n_experts, act);
     IDM_LAUNCH_CHECK("experts_gate_up");
-    idm_launch(experts_down_kernel, dim3(n_tokens, by2), dim3(256), s2, stream, (const float*)a, choice, (const T*)down, h, width,
+    idm_launch(experts_down_kernel, dim3(n_tokens, by2), dim3(256), s2, stream, (const float*)a, tokens, table, (const T*)down, h, width,
                ff, top, n_experts, weight);
     IDM_LAUNCH_CHECK("experts_down");
     return 0;
@@ -148,3 +177,28 @@ extern "C" int idm_experts_combine(const float* z, const int* place, float* h, i
     IDM_LAUNCH_CHECK("experts_combine");
     return 0;
 }
+
+#if defined(IDM_BF16)
+// Every expert's gated feed-forward over its slice of rows grouped by expert: the library's own matrix products (the
+// gate/up product with the activation as its epilogue, then the down product), expert after expert, from one call.
+// counts: on the HOST, rows of each expert; gate_up [E, tiles * 128, width] alternating rows; down [E, width, ff].
+extern "C" int idm_gemm_bf16_gated(const void* x, const void* w, void* y, int M, int inter, int K, int act, cudaStream_t stream);
+extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, int N, int K, cudaStream_t stream);
+
+extern "C" int idm_experts_grouped(const void* xg, const int* counts, int n_experts, const void* gate_up,
+                                   long long gate_up_stride, const void* down, long long down_stride, void* y, float* z,
+                                   int width, int ff, int act, cudaStream_t stream) {
+    IDM_REQUIRE(width > 0 && ff > 0 && width % 8 == 0 && ff % 8 == 0, "experts_grouped: width=%d ff=%d (multiples of 8)", width, ff);
+    long long at = 0;
+    for (int e = 0; e < n_experts; ++e) {
+        const int c = counts[e];
+        if (c <= 0) continue;
+        const T* xe = (const T*)xg + at * width;
+        T* ye = (T*)y + at * ff;
+        if (idm_gemm_bf16_gated(xe, (const T*)gate_up + (long long)e * gate_up_stride, ye, c, ff, width, act, stream)) return 1;
+        if (idm_gemm_bf16(ye, (const T*)down + (long long)e * down_stride, z + at * width, c, width, ff, stream)) return 1;
+        at += c;
+    }
+    return 0;
+}
+#endif

@@ -95,11 +95,12 @@ SIGNATURES = {
     "idm_latent_kv_finish": (c_int, "piiiiipfpifppippppip"),
     "idm_headwise": (c_int, "pqiipipiqiiipifiip"),
     "idm_latent_attention_max_rank": (c_int, ""),
+    "idm_latent_attention_heads_per_block": (c_int, "iii"),
     "idm_latent_attention": (c_int, "pppippppppiiiifiip"),
     "idm_latent_expand_pack": (c_int, "pippiiiiiipifippppipppip"),
-    "idm_experts_from_table": (c_int, "ppipip"),
-    "idm_experts_few": (c_int, "pppppppiiiiiifp"),
+    "idm_experts_few": (c_int, "ppppqqqpppiiiiiifp"),
     "idm_rows_gather": (c_int, "pppiip"),
+    "idm_experts_grouped": (c_int, "ppipqpqppiiip"),
     "idm_experts_combine": (c_int, "pppiiifp"),
     "idm_add_dyt": (c_int, "ppiqppfppiip"),
     "idm_act_cast": (c_int, "ppqip"),
@@ -690,13 +691,18 @@ class Kernels:
         xp[:, :x.shape[1]] = x
         return xp, wp
 
-    def gemm_store(self, x, w, pad: bool = False) -> torch.Tensor:
+    def gemm_store(self, x, w, pad: bool = False, out=None) -> torch.Tensor:
         """``x . w^T`` in 32-bit ``[M, N]``.  ``pad``: a bfloat16 inner size that is no multiple of 8 is served with
-        zero columns added to both operands instead of being refused."""
+        zero columns added to both operands instead of being refused.  ``out``: a contiguous 32-bit ``[M, N]`` to write."""
         if pad:
             x, w = self._padded(x, w)
         M, N, Kd = self._gemm_shape(x, w)
-        out = torch.empty((M, N), dtype=torch.float32, device=self.device)
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=self.device)
+        else:
+            self._need(out, torch.float32, "gemm output")
+            if tuple(out.shape) != (M, N):
+                raise KernelError(f"gemm: output {tuple(out.shape)} does not match the product {(M, N)}")
         if M:
             if self.dtype == torch.float32:
                 self._check(self.lib.idm_gemm_f32(_p(x), _p(w), _p(out), M, N, Kd, self._stream()))
@@ -885,7 +891,7 @@ class Kernels:
     def latent_attention(self, qa, kv, ctx, rank: int, scale: float, sink=None) -> torch.Tensor:
         """Causal attention of the step's queries ``qa [N, H, D]`` (32-bit, in the latent's space) over the cached rows
         ``[c | r]`` of ``D`` numbers; returns the context ``[N, H * rank]`` in 32-bit: the weighted sums of ``c``.
-        Steps of few tokens cut the keys into runs of 256 positions, a block each, that meet in scratch."""
+        Steps of few tokens cut the keys into runs of 64 to 256 positions, a block each, that meet in scratch."""
         self._need(qa, torch.float32, "latent queries")
         n, H, D = qa.shape
         if tuple(kv.k.shape[1:]) != (1, self.page, D):
@@ -896,7 +902,13 @@ class Kernels:
                 raise KernelError(f"{sink.numel()} sinks for {H} heads")
         out = torch.empty((n, H * rank), dtype=torch.float32, device=self.device)
         run_keys, n_runs, part = 256, 1, None
-        if n * (-(-H // 8)) < 2 * self.sm_count:
+        groups = n * (-(-H // self.lib.idm_latent_attention_heads_per_block(H, rank, D)))      # blocks per run
+        if groups < 2 * self.sm_count:
+            # runs short enough to give the step about four blocks per SM, of 64 to 256 keys (whole pages); the
+            # choice depends on the step's shape and the cache's limit only, never on a sequence's length
+            fair = -(-ctx.max_kv_len * groups // (4 * self.sm_count))
+            run_keys = min(256, max(64, -(-fair // 64) * 64))
+            run_keys = max(run_keys, -(-ctx.max_kv_len // (512 * 64)) * 64)       # (at most 512 runs)
             n_runs = max(1, -(-ctx.max_kv_len // run_keys))
         if n_runs > 1:
             part = self.scratch("latent_attention", n * H * n_runs * (rank + 2))
@@ -921,26 +933,25 @@ class Kernels:
         return q, k, v
 
     # ---- experts chosen per token -------------------------------------------------------------------
-    def experts_from_table(self, tokens, table) -> torch.Tensor:
-        """``table[tokens]``: the experts ``[N, top]`` of the step's tokens from a table by token id."""
-        self._need(tokens, torch.int32, "tokens")
-        self._need(table, torch.int32, "expert table")
-        n, top = tokens.numel(), table.shape[1]
-        choice = torch.empty((n, top), dtype=torch.int32, device=self.device)
-        self._check(self.lib.idm_experts_from_table(_p(tokens), _p(table), top, _p(choice), n, self._stream()))
-        return choice
-
-    def experts_few(self, x, choice, gate, up, down, h, act: int, weight: float) -> None:
-        """``h[t] += weight * sum_k down[e] (act(gate[e] x_t) * up[e] x_t)``, ``e = choice[t, k]``: every (token, choice)
-        streams its expert's matrices (steps of few tokens)."""
+    def experts_few(self, x, tokens, table, gate_up, row_stride: int, up_off: int, down, h, act: int, weight: float) -> None:
+        """``h[t] += weight * sum_k down[e] (act(gate[e] x_t) * up[e] x_t)``, ``e = table[tokens[t], k]``: every (token, choice)
+        streams its expert's matrices (steps of few tokens).  ``gate_up [E, rows, width]`` holds an expert's gate and up
+        rows: gate row f starts ``f * row_stride`` elements into the expert's block and its up row ``up_off`` behind it.
+        ``down [E, width, ff]``."""
         self._need(x, self.dtype, "experts input")
         self._need(h, torch.float32, "residual stream")
+        self._need(gate_up, self.dtype, "experts' gate and up rows")
+        self._need(down, self.dtype, "experts' down matrices")
+        self._need(tokens, torch.int32, "tokens")
+        self._need(table, torch.int32, "expert table")
         n, width = x.shape
-        E, ff, _ = gate.shape
-        top = choice.shape[1]
+        E, _, ff = down.shape
+        top = table.shape[1]
+        if gate_up.shape[0] != E or gate_up.shape[2] != width or (ff - 1) * row_stride + up_off + width > gate_up.shape[1] * width:
+            raise KernelError(f"experts: gate/up rows {tuple(gate_up.shape)} do not hold {ff} rows at stride {row_stride} + {up_off}")
         a = torch.empty((n, top, ff), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_experts_few(_p(x), _p(choice), _p(gate), _p(up), _p(down), _p(a), _p(h), n, width, ff, top, E,
-                                             act, float(weight), self._stream()), 2)
+        self._check(self.lib.idm_experts_few(_p(x), _p(tokens), _p(table), _p(gate_up), gate_up.shape[1] * width, row_stride, up_off, _p(down),
+                                             _p(a), _p(h), n, width, ff, top, E, act, float(weight), self._stream()), 2)
 
     def rows_gather(self, x, src) -> torch.Tensor:
         self._need(x, self.dtype, "rows")
@@ -948,6 +959,21 @@ class Kernels:
         out = torch.empty((src.numel(), x.shape[1]), dtype=self.dtype, device=self.device)
         self._check(self.lib.idm_rows_gather(_p(x), _p(src), _p(out), src.numel(), x.shape[1], self._stream()))
         return out
+
+    def experts_grouped(self, xg, counts, gate_up, down, act: int) -> torch.Tensor:
+        """Rows grouped by expert (``counts[e]`` rows of expert e, one group after another) through every expert's gated
+        feed-forward: ``z[rows of e] = down[e] (act(gate[e] x) * up[e] x)``, 32-bit ``[rows, width]``.  One call: the
+        library runs the two matrix products of every expert that has rows (``gate_up`` in the layout of
+        ``tile_gate_up``).  ``counts``: a contiguous int32 numpy array on the host."""
+        self._need(xg, self.dtype, "grouped rows")
+        rows, width = xg.shape
+        E, _, ff = down.shape
+        y = torch.empty((rows, ff), dtype=self.dtype, device=self.device)
+        z = torch.empty((rows, width), dtype=torch.float32, device=self.device)
+        with_rows = int((counts > 0).sum())
+        self._check(self.lib.idm_experts_grouped(_p(xg), counts.ctypes.data, E, _p(gate_up), gate_up.shape[1] * width, _p(down),
+                                                 width * ff, _p(y), _p(z), width, ff, act, self._stream()), 2 * with_rows)
+        return z
 
     def experts_combine(self, z, place, h, weight: float) -> None:
         """``h[t] += weight * sum_k z[place[t, k]]`` in ascending k (``place`` < 0: nothing)."""

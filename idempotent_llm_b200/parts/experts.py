@@ -44,26 +44,26 @@ class TableExperts(FeedForward):
         self.spec, self.rt, self.act = spec, rt, ACTIVATIONS[s.activation]
 
         def stack(name):
-            return torch.stack([weights[prefix + s.expert.format(e) + name].to(rt.dtype) for e in range(s.n_experts)]).contiguous()
-        self.gate, self.up, self.down = stack(nm.gate), stack(nm.up), stack(nm.down)     # [E, ff, W], [E, ff, W], [E, W, ff]
+            return [weights[prefix + s.expert.format(e) + name].to(rt.dtype) for e in range(s.n_experts)]
+        K = rt.kernels
+        aligned = not (rt.dtype == torch.bfloat16 and (s.hidden % 8 or s.intermediate % 8))
+        self.fused = bool(getattr(K, "fused", False)) and aligned
+        self.can_group = aligned
+        # An expert's gate and up rows are ONE matrix, which both kinds of step read: alternating (gate row of a
+        # feature, then its up row: what the gated product's epilogue wants) with the fused kernels, else gate rows
+        # followed by up rows.  [E, rows, W]; down [E, W, ff].
+        if self.fused:
+            self.gate_up = torch.stack([K.tile_gate_up(g, u) for g, u in zip(stack(nm.gate), stack(nm.up))]).contiguous()
+            self.row_stride, self.up_off = 2 * s.hidden, s.hidden
+        else:
+            self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(stack(nm.gate), stack(nm.up))]).contiguous()
+            self.row_stride, self.up_off = s.hidden, s.intermediate * s.hidden
+        self.down = torch.stack(stack(nm.down)).contiguous()
         self.table = weights[prefix + s.table].to(torch.int32).contiguous()
         self.table_host = self.table.cpu().numpy()
         bad = (self.table_host < 0) | (self.table_host >= s.n_experts)
         if bad.any():
             raise ValueError(f"{prefix + s.table}: entries outside the {s.n_experts} experts")
-        K = rt.kernels
-        aligned = not (rt.dtype == torch.bfloat16 and (s.hidden % 8 or s.intermediate % 8))
-        self.fused = bool(getattr(K, "fused", False)) and aligned
-        self.can_group = aligned
-        # for the grouped path: gate and up of an expert as one matrix, in the layout its product's epilogue reads
-        self._gate_up = None
-
-    def _gate_up_of(self, e: int):
-        if self._gate_up is None:
-            K = self.rt.kernels
-            self._gate_up = [K.tile_gate_up(self.gate[i], self.up[i]) if self.fused
-                             else torch.cat([self.gate[i], self.up[i]], dim=0).contiguous() for i in range(self.spec.n_experts)]
-        return self._gate_up[e]
 
     def forward(self, x, ctx, residual=None):
         """Adds into ``residual`` and returns None (or returns the delta ``[1, N, hidden]``)."""
@@ -74,8 +74,7 @@ class TableExperts(FeedForward):
         if toks is not None and self.can_group and n * s.top >= GROUP_FROM:
             self._grouped(x, np.concatenate([np.asarray(t, dtype=np.int64) for t in toks]), h)
         else:
-            choice = K.experts_from_table(ctx.tokens, self.table)
-            K.experts_few(x, choice, self.gate, self.up, self.down, h, self.act, 1.0 / s.top)
+            K.experts_few(x, ctx.tokens, self.table, self.gate_up, self.row_stride, self.up_off, self.down, h, self.act, 1.0 / s.top)
         return None if residual is not None else h.unsqueeze(0)
 
     def _grouped(self, x, tokens, h):
@@ -88,6 +87,10 @@ class TableExperts(FeedForward):
         place[order] = np.arange(n * top, dtype=np.int32)                  # (token, k) -> grouped row
         both = torch.from_numpy(np.concatenate([(order // top).astype(np.int32), place])).to(x.device, non_blocking=True)
         xg = K.rows_gather(x, both[:n * top])
+        if self.fused:                      # every expert's two products from one call into the library
+            z = K.experts_grouped(xg, np.ascontiguousarray(counts, dtype=np.int32), self.gate_up, self.down, self.act)
+            K.experts_combine(z, both[n * top:].view(n, top), h, 1.0 / top)
+            return
         z = torch.empty((n * top, s.hidden), dtype=torch.float32, device=x.device)
         at = 0
         for e in range(s.n_experts):
@@ -96,9 +99,9 @@ class TableExperts(FeedForward):
                 continue
             xe = xg[at:at + c]
             if self.fused:
-                y = K.gemm_gated(xe, self._gate_up_of(e), s.intermediate, self.act)
+                y = K.gemm_gated(xe, self.gate_up[e], s.intermediate, self.act)
             else:
-                y = K.gated_act(K.gemm_store(xe, self._gate_up_of(e)), self.act)
-            z[at:at + c] = K.gemm_store(y, self.down[e])
+                y = K.gated_act(K.gemm_store(xe, self.gate_up[e]), self.act)
+            K.gemm_store(y, self.down[e], out=z[at:at + c])
             at += c
         K.experts_combine(z, both[n * top:].view(n, top), h, 1.0 / top)
