@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
-            const int r = place[t * top + k];
+            const int r = place ? place[t * top + k] : (int)(t * top + k);      // (no places: pair by pair as they lie)
             if (r >= 0) s += z[(size_t)r * width + d];
         }
         h[t * width + d] += s * weight;
@@ -174,6 +174,142 @@ extern "C" int idm_experts_combine(const float* z, const int* place, float* h, i
                                    float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, z, place, h, width, top, weight);
+    IDM_LAUNCH_CHECK("experts_combine");
+    return 0;
+}
+
+// ------------------------------------------------------------------ the same, expert by expert
+// For steps of more than a few tokens whose ids exist on the device only: a block has one expert and a slice of its
+// rows, finds the (token, choice) pairs that use the expert (in ascending order), and walks them eight at a time: the
+// eight input vectors wait in shared memory, a warp streams a row of the expert's matrix once for all eight.  An expert
+// is read from memory once a step however many tokens use it.  MODE 0: a[pair, f] = act(gate[f] . x_t) * (up[f] . x_t);
+// MODE 1: z[pair, w] = down[w] . a[pair].  Sums in 32-bit, lanes over the inner axis, then a butterfly.
+#define EX_TOKENS 8
+
+template <int MODE>
+__global__ void __launch_bounds__(256) experts_major_kernel(const T* __restrict__ x, const float* __restrict__ a_in,
+                                                            const int* __restrict__ tokens, const int* __restrict__ table,
+                                                            const T* __restrict__ w, long long expert_stride, long long row_stride,
+                                                            long long up_off, float* __restrict__ out, int n_tokens, int top,
+                                                            int K, int rows, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    float* xs = sm;                                              // [EX_TOKENS][K]
+    int* pairs = reinterpret_cast<int*>(sm + EX_TOKENS * K);     // [n_tokens * top]
+    __shared__ int count_s;
+    const int e = blockIdx.x, wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (wib == 0) {                                              // the pairs of this expert, in ascending order
+        int count = 0;
+        for (int p0 = 0; p0 < n_tokens * top; p0 += 32) {
+            const int p = p0 + lane;
+            const bool mine = p < n_tokens * top && table[(size_t)tokens[p / top] * top + p % top] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) pairs[count + __popc(m & ((1u << lane) - 1u))] = p;
+            count += __popc(m);
+        }
+        if (lane == 0) count_s = count;
+    }
+    __syncthreads();
+    const int count = count_s;
+    if (count == 0) return;
+    const bool vec = (K * (int)sizeof(T)) % 16 == 0;
+    const T* we = w + (size_t)e * expert_stride;
+    for (int p0 = 0; p0 < count; p0 += EX_TOKENS) {
+        const int np = min(EX_TOKENS, count - p0);
+        __syncthreads();                                         // the last eight's readers are done
+        for (int i = threadIdx.x; i < EX_TOKENS * K; i += blockDim.x) {
+            const int tt = i / K, d = i % K;
+            float v = 0.f;
+            if (tt < np) {
+                const int p = pairs[p0 + tt];
+                v = MODE == 0 ? to_f32(x[(size_t)(p / top) * K + d]) : a_in[(size_t)p * K + d];
+            }
+            xs[i] = v;
+        }
+        __syncthreads();
+        for (int r = blockIdx.y * 8 + wib; r < rows; r += gridDim.y * 8) {
+            const T* w0 = we + (size_t)r * row_stride;
+            float g[EX_TOKENS], u[EX_TOKENS];
+#pragma unroll
+            for (int tt = 0; tt < EX_TOKENS; ++tt) g[tt] = u[tt] = 0.f;
+            if (vec) {
+                constexpr int VN = Vec16<T>::N;
+                // four 16-byte pieces of the row (and of its partner) per lane are requested before the first is used
+                for (int d0 = lane * VN; d0 < K; d0 += 4 * 32 * VN) {
+                    Vec16<T> wg[4], wu[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int d = d0 + c * 32 * VN;
+                        if (d < K) {
+                            wg[c].load(w0 + d);
+                            if (MODE == 0) wu[c].load(w0 + up_off + d);
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int d = d0 + c * 32 * VN;
+                        if (d < K) {
+#pragma unroll
+                            for (int tt = 0; tt < EX_TOKENS; ++tt) {
+#pragma unroll
+                                for (int q = 0; q < VN; q += 4) {
+                                    const float4 xv = *reinterpret_cast<const float4*>(xs + tt * K + d + q);
+                                    g[tt] = fmaf(xv.x, wg[c].get(q), g[tt]); g[tt] = fmaf(xv.y, wg[c].get(q + 1), g[tt]);
+                                    g[tt] = fmaf(xv.z, wg[c].get(q + 2), g[tt]); g[tt] = fmaf(xv.w, wg[c].get(q + 3), g[tt]);
+                                    if (MODE == 0) {
+                                        u[tt] = fmaf(xv.x, wu[c].get(q), u[tt]); u[tt] = fmaf(xv.y, wu[c].get(q + 1), u[tt]);
+                                        u[tt] = fmaf(xv.z, wu[c].get(q + 2), u[tt]); u[tt] = fmaf(xv.w, wu[c].get(q + 3), u[tt]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int d = lane; d < K; d += 32) {
+                    const float wg = to_f32(w0[d]), wu = MODE == 0 ? to_f32(w0[up_off + d]) : 0.f;
+#pragma unroll
+                    for (int tt = 0; tt < EX_TOKENS; ++tt) {
+                        g[tt] = fmaf(xs[tt * K + d], wg, g[tt]);
+                        if (MODE == 0) u[tt] = fmaf(xs[tt * K + d], wu, u[tt]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int tt = 0; tt < EX_TOKENS; ++tt) {
+                g[tt] = warp_sum(g[tt]);
+                if (MODE == 0) u[tt] = warp_sum(u[tt]);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int tt = 0; tt < EX_TOKENS; ++tt)
+                    if (tt < np) out[(size_t)pairs[p0 + tt] * rows + r] = MODE == 0 ? gated_act(g[tt], u[tt], act) : g[tt];
+            }
+        }
+    }
+}
+
+// z: [n_tokens * top, width] 32-bit scratch for the experts' outputs (then added to h pair by pair in ascending k)
+extern "C" int idm_experts_major(const void* x, const int* tokens, const int* table, const void* gate_up,
+                                 long long expert_stride, long long row_stride, long long up_off, const void* down,
+                                 float* a, float* z, float* h, int n_tokens, int width, int ff, int top, int n_experts,
+                                 int act, float weight, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(width > 0 && ff > 0 && top > 0 && n_experts > 0 && (act == 0 || act == 1), "experts: width=%d ff=%d top=%d experts=%d act=%d",
+                width, ff, top, n_experts, act);
+    const size_t s1 = (size_t)EX_TOKENS * width * 4 + (size_t)n_tokens * top * 4, s2 = (size_t)EX_TOKENS * ff * 4 + (size_t)n_tokens * top * 4;
+    IDM_REQUIRE(s1 <= 200 * 1024 && s2 <= 200 * 1024, "experts: width=%d or ff=%d with %d tokens does not fit shared memory", width, ff, n_tokens);
+    if (s1 > 48 * 1024) cudaFuncSetAttribute(experts_major_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1);
+    if (s2 > 48 * 1024) cudaFuncSetAttribute(experts_major_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s2);
+    const int by1 = max(1, min((ff + 7) / 8, 592 / n_experts)), by2 = max(1, min((width + 7) / 8, 592 / n_experts));
+    idm_launch(experts_major_kernel<0>, dim3(n_experts, by1), dim3(256), s1, stream, (const T*)x, (const float*)nullptr, tokens, table,
+               (const T*)gate_up, expert_stride, row_stride, up_off, a, n_tokens, top, width, ff, act);
+    IDM_LAUNCH_CHECK("experts_major gate/up");
+    idm_launch(experts_major_kernel<1>, dim3(n_experts, by2), dim3(256), s2, stream, (const T*)nullptr, (const float*)a, tokens, table,
+               (const T*)down, (long long)width * ff, (long long)ff, 0LL, z, n_tokens, top, ff, width, act);
+    IDM_LAUNCH_CHECK("experts_major down");
+    idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z, (const int*)nullptr, h, width, top, weight);
     IDM_LAUNCH_CHECK("experts_combine");
     return 0;
 }

@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(HW_WARPS * 32) headwise_kernel(const float* __
     for (int tt = 0; tt < HW_TOKENS; ++tt) acc[tt] = 0.f;
     if (o < O) {
         const T* Wh = W + (size_t)h * I * O + o;
-#pragma unroll 4
+#pragma unroll 8
         for (int i = i0; i < i1; ++i) {
             const float wv = to_f32(Wh[(size_t)i * O]);
 #pragma unroll
@@ -542,48 +542,54 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
 }
 #endif
 
-// one warp per (token, head): the runs' maxima and sums are gathered a run per lane, every run's weight is computed
-// once and kept in shared memory, and a lane adds its columns of the runs' contexts in ascending order of the runs
-// (four loads in flight); the sink joins the sum once
+// one block per (token, head): the runs' maxima and sums are gathered by the first warp, a run per lane, every run's
+// weight is computed once and kept in shared memory, and a thread adds its columns of the runs' contexts in ascending
+// order of the runs (eight loads in flight); the sink joins the sum once
 #define LF_MAX_RUNS 512
-__global__ void __launch_bounds__(128) latent_fold_kernel(const float* __restrict__ part, const float* __restrict__ sink,
-                                                          float* __restrict__ ctx, const int* __restrict__ positions,
-                                                          int n_tokens, int H, int R, int run_keys, int n_runs) {
+#define LF_THREADS 256
+__global__ void __launch_bounds__(LF_THREADS) latent_fold_kernel(const float* __restrict__ part, const float* __restrict__ sink,
+                                                                 float* __restrict__ ctx, const int* __restrict__ positions,
+                                                                 int n_tokens, int H, int R, int run_keys, int n_runs) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float wts[4][LF_MAX_RUNS];
-    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long w = (long long)blockIdx.x * 4 + wib;
-    if (w >= (long long)n_tokens * H) return;                                 // whole warps leave; no block barrier below
+    __shared__ float wts[LF_MAX_RUNS];
+    __shared__ float inv_s;
+    const int lane = threadIdx.x & 31;
+    const long long w = blockIdx.x;
     const int t = (int)(w / H), head = (int)(w % H);
     const int used = min(n_runs, positions[t] / run_keys + 1);               // runs that hold keys of this query
     const size_t stride = (size_t)R + 2;
     const float* p = part + (size_t)w * n_runs * stride;
-    const float sk = sink ? sink[head] : -INFINITY;
-    float mf = sk;
-    for (int r = lane; r < used; r += 32) mf = fmaxf(mf, p[r * stride]);
-    mf = warp_max(mf);
-    float l = 0.f;
-    for (int r = lane; r < used; r += 32) {
-        const float wr = expf(p[r * stride] - mf);
-        wts[wib][r] = wr;
-        l = fmaf(p[r * stride + 1], wr, l);
+    if (threadIdx.x < 32) {
+        const float sk = sink ? sink[head] : -INFINITY;
+        float mf = sk;
+        for (int r = lane; r < used; r += 32) mf = fmaxf(mf, p[r * stride]);
+        mf = warp_max(mf);
+        float l = 0.f;
+        for (int r = lane; r < used; r += 32) {
+            const float wr = expf(p[r * stride] - mf);
+            wts[r] = wr;
+            l = fmaf(p[r * stride + 1], wr, l);
+        }
+        l = warp_sum(l);
+        if (sink) l += expf(sk - mf);
+        if (lane == 0) inv_s = 1.0f / l;
     }
-    l = warp_sum(l);
-    if (sink) l += expf(sk - mf);
-    const float inv = 1.0f / l;
-    __syncwarp();
+    __syncthreads();
+    const float inv = inv_s;
     float* o = ctx + (size_t)w * R;
-    for (int d = lane; d < R; d += 32) {
+    for (int d = threadIdx.x; d < R; d += LF_THREADS) {
         const float* pd = p + 2 + d;
         float s = 0.f;
         int r = 0;
-        for (; r + 4 <= used; r += 4) {
-            const float v0 = pd[r * stride], v1 = pd[(r + 1) * stride], v2 = pd[(r + 2) * stride], v3 = pd[(r + 3) * stride];
-            s = fmaf(v0, wts[wib][r], s); s = fmaf(v1, wts[wib][r + 1], s);
-            s = fmaf(v2, wts[wib][r + 2], s); s = fmaf(v3, wts[wib][r + 3], s);
+        for (; r + 8 <= used; r += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = pd[(r + i) * stride];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(v[i], wts[r + i], s);
         }
-        for (; r < used; ++r) s = fmaf(pd[r * stride], wts[wib][r], s);
+        for (; r < used; ++r) s = fmaf(pd[r * stride], wts[r], s);
         o[d] = s * inv;
     }
 }
@@ -638,8 +644,7 @@ extern "C" int idm_latent_attention(const float* qa, const void* pool, const int
 #undef LM_LAUNCH
         IDM_LAUNCH_CHECK("latent_attention_mma");
         if (n_runs > 1) {
-            const long long warps = (long long)n_tokens * H;
-            idm_launch(latent_fold_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part, sink, ctx,
+            idm_launch(latent_fold_kernel, dim3((unsigned)(n_tokens * H)), dim3(LF_THREADS), 0, stream, (const float*)part, sink, ctx,
                        positions, n_tokens, H, R, run_keys, n_runs);
             IDM_LAUNCH_CHECK("latent_fold");
         }
@@ -676,8 +681,7 @@ extern "C" int idm_latent_attention(const float* qa, const void* pool, const int
 #undef LA_LAUNCH_H
     IDM_LAUNCH_CHECK("latent_attention");
     if (n_runs > 1) {
-        const long long warps = (long long)n_tokens * H;
-        idm_launch(latent_fold_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part, sink, ctx,
+        idm_launch(latent_fold_kernel, dim3((unsigned)(n_tokens * H)), dim3(LF_THREADS), 0, stream, (const float*)part, sink, ctx,
                    positions, n_tokens, H, R, run_keys, n_runs);
         IDM_LAUNCH_CHECK("latent_fold");
     }

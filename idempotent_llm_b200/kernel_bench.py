@@ -16,6 +16,8 @@ def run(args) -> int:
     cfg = preset(args.size)
     if args.kernel == "ssd_mixer":
         return ssd_mixer(args, cfg)
+    if args.kernel == "latent_mixer":
+        return latent_mixer(args, cfg)
     K = Kernels(torch.bfloat16, "cuda:0")
     # which kernel a product of many tokens takes (defaults: what the library chooses by itself)
     K.gemm_choices(pair=None if getattr(args, "pairs", None) is None else bool(args.pairs),
@@ -144,6 +146,97 @@ def ssd_mixer(args, cfg) -> int:
         torch.cuda.synchronize()
         if i >= 3:
             print(f"ssd mixer, {B} x {T} tokens: {e0.elapsed_time(e1) * 1e3:.1f} us")
+    return 0
+
+
+def latent_mixer(args, cfg) -> int:
+    """The kernels of a latent attention layer and of a table-routed feed-forward alone, at a Panodra preset's sizes
+    (``--size panodra-0.6b``): single tokens of ``--batch`` sequences holding about ``--context`` tokens, and whole
+    prompts of ``--context`` tokens; every kernel timed by itself with the L2 flushed, with the bytes it has to move."""
+    from .cache import SequenceCache
+    from .engine.batch import context_from_packed, pack_step_host
+    from .kernels import Kernels
+    from .parts import FEED_FORWARDS, MIXERS, Runtime
+    from .weights import random_weights
+    spec_m = cfg.to_model_spec()
+    s = spec_m.layers[0].mixer
+    ffs = next((L.feed_forward for L in spec_m.layers if getattr(L.feed_forward, "kind", "") == "table_experts"), None)
+    dev = torch.device("cuda:0")
+    K = Kernels(torch.bfloat16, dev)
+    rt = Runtime(device=dev, dtype=torch.bfloat16, kernels=K)
+    cls = MIXERS.get(s.kind)
+    mixer = cls(s, random_weights(cls.declare(s, "m."), 1, 0.02, dtype=torch.bfloat16, device="cuda"), "m.", rt)
+    B, T, cap = args.batch, args.context, args.capacity
+    H, R, D = s.n_heads, s.kv_rank, s.kv_rank + s.rot_dim
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(args.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def say(name, t, nbytes):
+        print(f"{name:34s} {t * 1e6:8.1f} us  {nbytes / 1e6:9.2f} MB  {nbytes / t / 1e9:8.0f} GB/s")
+
+    cache = SequenceCache({0: cls.cache_need(s)}, B * cap, torch.bfloat16, dev, max_seqs=B, max_seq_len=cap)
+    slots = [cache.alloc_slot() for _ in range(B)]
+    lens = [int(torch.randint(int(T * 0.7), T + 1, (1,), generator=g)) for _ in range(B)]
+    cache.reserve(list(zip(slots, lens))); cache.flush()
+    kv = cache.view(0)
+    kv.k.normal_()
+    ids = [[int(torch.randint(0, cfg.vocab, (1,), generator=g))] for _ in range(B)]
+    packed, n, q_lens = pack_step_host(slots, [L - 1 for L in lens], ids)
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [L - 1 for L in lens], max_kv_len=cap)
+    x = torch.randn(B, s.hidden, device="cuda").bfloat16()
+    proj = K.gemm_store(x, mixer.w_in)
+    cs = mixer.position.tables(ctx)
+    qa = K.headwise(proj, 0, H, s.plain_dim + s.rot_dim, mixer.uk, tail=s.rot_dim, rot_dims=mixer.rot_dims, cs=cs, out_f32=True)
+    c = K.latent_attention(qa, kv, ctx, R, s.softmax_scale, sink=mixer.sink)
+    print(f"single tokens: {B} sequences of {min(lens)}..{max(lens)} tokens, {H} heads, latent {R} + {s.rot_dim}")
+    say("joint input product", timed(lambda: K.gemm_store(x, mixer.w_in)), mixer.w_in.numel() * 2)
+    say("queries into the latent's space", timed(lambda: K.headwise(proj, 0, H, s.plain_dim + s.rot_dim, mixer.uk, tail=s.rot_dim,
+                                                                  rot_dims=mixer.rot_dims, cs=cs, out_f32=True)), mixer.uk.numel() * 2)
+    say("attention over the latent rows", timed(lambda: K.latent_attention(qa, kv, ctx, R, s.softmax_scale, sink=mixer.sink)),
+        sum(lens) * D * 2)
+    say("values out of the latent's space", timed(lambda: K.headwise(c, 0, H, R, mixer.uv_t)), mixer.uv_t.numel() * 2)
+    if ffs is not None:
+        fcls = FEED_FORWARDS.get(ffs.kind)
+        ff = fcls(ffs, random_weights(fcls.declare(ffs, "f."), 2, 0.02, dtype=torch.bfloat16, device="cuda"), "f.", rt)
+        h = torch.zeros(B, ffs.hidden, device="cuda")
+        used = len({int(e) for t in ids for e in ff.table_host[t[0]]})
+        nbytes = used * 3 * ffs.hidden * ffs.intermediate * 2
+        say(f"experts ({ffs.top} of {ffs.n_experts}, {used} used)", timed(lambda: ff.forward(x, ctx, residual=h)), nbytes)
+        major, K.EXPERT_MAJOR_FROM = K.EXPERT_MAJOR_FROM, 1 << 30
+        say("  the same, token by token", timed(lambda: ff.forward(x, ctx, residual=h)), nbytes)
+        K.EXPERT_MAJOR_FROM = major
+    # whole prompts
+    for sl in slots:
+        cache.free_slot(sl)
+    P = max(1, min(B, cap * B // max(T, 1)))
+    slots = [cache.alloc_slot() for _ in range(P)]
+    cache.reserve([(sl, T) for sl in slots]); cache.flush()
+    toks = [[int(v) for v in torch.randint(0, cfg.vocab, (T,), generator=g)] for _ in range(P)]
+    packed, n, q_lens = pack_step_host(slots, [0] * P, toks)
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [0] * P, host_tokens=toks)
+    x = torch.randn(P * T, s.hidden, device="cuda").bfloat16()
+    hres = torch.zeros(P * T, s.hidden, device="cuda")
+    t = timed(lambda: (ctx.memo.clear(), mixer.forward(x, ctx, cache.view(0), None, True, residual=hres)))
+    flops = 2.0 * P * T * (s.hidden * mixer.w_in.shape[0] + R * H * (s.plain_dim + s.value_dim) + H * s.value_dim * s.hidden) \
+        + P * H * 2.0 * (s.plain_dim + s.rot_dim + s.value_dim) * T * (T + 1)
+    print(f"whole prompts: {P} x {T} tokens: latent attention layer {t * 1e6:.1f} us, {flops / t / 1e12:.0f} TFLOP/s")
+    if ffs is not None:
+        t = timed(lambda: ff.forward(x, ctx, residual=hres))
+        fl = 2.0 * P * T * ffs.top * 3 * ffs.hidden * ffs.intermediate
+        print(f"whole prompts: experts grouped by expert {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s")
     return 0
 
 

@@ -99,6 +99,7 @@ SIGNATURES = {
     "idm_latent_attention": (c_int, "pppippppppiiiifiip"),
     "idm_latent_expand_pack": (c_int, "pippiiiiiipifippppipppip"),
     "idm_experts_few": (c_int, "ppppqqqpppiiiiiifp"),
+    "idm_experts_major": (c_int, "ppppqqqppppiiiiiifp"),
     "idm_rows_gather": (c_int, "pppiip"),
     "idm_experts_grouped": (c_int, "ppipqpqppiiip"),
     "idm_experts_combine": (c_int, "pppiiifp"),
@@ -933,6 +934,9 @@ class Kernels:
         return q, k, v
 
     # ---- experts chosen per token -------------------------------------------------------------------
+    # from this many (token, choice) pairs on, a step of few tokens walks its experts one by one
+    EXPERT_MAJOR_FROM = 64
+
     def experts_few(self, x, tokens, table, gate_up, row_stride: int, up_off: int, down, h, act: int, weight: float) -> None:
         """``h[t] += weight * sum_k down[e] (act(gate[e] x_t) * up[e] x_t)``, ``e = table[tokens[t], k]``: every (token, choice)
         streams its expert's matrices (steps of few tokens).  ``gate_up [E, rows, width]`` holds an expert's gate and up
@@ -950,6 +954,13 @@ class Kernels:
         if gate_up.shape[0] != E or gate_up.shape[2] != width or (ff - 1) * row_stride + up_off + width > gate_up.shape[1] * width:
             raise KernelError(f"experts: gate/up rows {tuple(gate_up.shape)} do not hold {ff} rows at stride {row_stride} + {up_off}")
         a = torch.empty((n, top, ff), dtype=torch.float32, device=self.device)
+        if n * top > self.EXPERT_MAJOR_FROM and max(width, ff) * 32 + n * top * 4 <= 200 * 1024:
+            # more pairs than a few: expert by expert, so that an expert's matrices are read once a step
+            z = torch.empty((n * top, width), dtype=torch.float32, device=self.device)
+            self._check(self.lib.idm_experts_major(_p(x), _p(tokens), _p(table), _p(gate_up), gate_up.shape[1] * width, row_stride,
+                                                   up_off, _p(down), _p(a), _p(z), _p(h), n, width, ff, top, E, act, float(weight),
+                                                   self._stream()), 3)
+            return
         self._check(self.lib.idm_experts_few(_p(x), _p(tokens), _p(table), _p(gate_up), gate_up.shape[1] * width, row_stride, up_off, _p(down),
                                              _p(a), _p(h), n, width, ff, top, E, act, float(weight), self._stream()), 2)
 

@@ -72,7 +72,10 @@ class TableExperts(FeedForward):
         h = residual if residual is not None else torch.zeros((n, s.hidden), dtype=torch.float32, device=x.device)
         toks = getattr(ctx, "host_tokens", None)
         if toks is not None and self.can_group and n * s.top >= GROUP_FROM:
-            self._grouped(x, np.concatenate([np.asarray(t, dtype=np.int64) for t in toks]), h)
+            ids = ctx.memo.get("host_token_array")           # the step's token ids as one array, made once a step
+            if ids is None:
+                ids = ctx.memo["host_token_array"] = np.concatenate([np.asarray(t, dtype=np.int64) for t in toks])
+            self._grouped(x, ids, h)
         else:
             K.experts_few(x, ctx.tokens, self.table, self.gate_up, self.row_stride, self.up_off, self.down, h, self.act, 1.0 / s.top)
         return None if residual is not None else h.unsqueeze(0)
