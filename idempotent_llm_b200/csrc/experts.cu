@@ -337,4 +337,39 @@ extern "C" int idm_experts_grouped(const void* xg, const int* counts, int n_expe
     }
     return 0;
 }
+
+// Single-token steps of many sequences, whose ids exist on the device only and whose shapes must not change from
+// step to step: EVERY expert's feed-forward over ALL the step's tokens with the library's matrix products (what such a
+// step has to do anyway is to stream every expert's matrices once: the products it does not need ride along), then
+// each token takes the outputs of its own experts.  z_all: [E, n_tokens, width] 32-bit; y: [n_tokens, ff] scratch.
+__global__ void __launch_bounds__(256) experts_pick_kernel(const float* __restrict__ z_all, const int* __restrict__ tokens,
+                                                           const int* __restrict__ table, float* __restrict__ h, int n_tokens,
+                                                           int width, int top, int n_experts, float weight) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = table[(size_t)tokens[t] * top + k];
+            if (e >= 0 && e < n_experts) s += z_all[((size_t)e * n_tokens + t) * width + d];
+        }
+        h[t * width + d] += s * weight;
+    }
+}
+
+extern "C" int idm_experts_dense(const void* x, const int* tokens, const int* table, int n_experts, const void* gate_up,
+                                 long long gate_up_stride, const void* down, long long down_stride, void* y, float* z_all,
+                                 float* h, int n_tokens, int width, int ff, int top, int act, float weight, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(width > 0 && ff > 0 && width % 8 == 0 && ff % 8 == 0, "experts_dense: width=%d ff=%d (multiples of 8)", width, ff);
+    for (int e = 0; e < n_experts; ++e) {
+        if (idm_gemm_bf16_gated(x, (const T*)gate_up + (long long)e * gate_up_stride, y, n_tokens, ff, width, act, stream)) return 1;
+        if (idm_gemm_bf16(y, (const T*)down + (long long)e * down_stride, z_all + (size_t)e * n_tokens * width, n_tokens, width, ff, stream)) return 1;
+    }
+    idm_launch(experts_pick_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z_all, tokens, table, h, n_tokens, width, top,
+               n_experts, weight);
+    IDM_LAUNCH_CHECK("experts_pick");
+    return 0;
+}
 #endif

@@ -102,6 +102,7 @@ SIGNATURES = {
     "idm_experts_major": (c_int, "ppppqqqppppiiiiiifp"),
     "idm_rows_gather": (c_int, "pppiip"),
     "idm_experts_grouped": (c_int, "ppipqpqppiiip"),
+    "idm_experts_dense": (c_int, "pppipqpqpppiiiiifp"),
     "idm_experts_combine": (c_int, "pppiiifp"),
     "idm_add_dyt": (c_int, "ppiqppfppiip"),
     "idm_act_cast": (c_int, "ppqip"),
@@ -985,6 +986,20 @@ class Kernels:
         self._check(self.lib.idm_experts_grouped(_p(xg), counts.ctypes.data, E, _p(gate_up), gate_up.shape[1] * width, _p(down),
                                                  width * ff, _p(y), _p(z), width, ff, act, self._stream()), 2 * with_rows)
         return z
+
+    def experts_dense(self, x, tokens, table, gate_up, down, h, act: int, weight: float) -> None:
+        """``h[t] += weight * sum_k ff_e(x_t)``, ``e = table[tokens[t], k]``, by running EVERY expert over all the step's
+        tokens with the library's matrix products and letting each token pick its own (single-token steps of many
+        sequences: every expert's matrices are streamed once, in shapes that do not change from step to step)."""
+        self._need(x, self.dtype, "experts input")
+        self._need(h, torch.float32, "residual stream")
+        n, width = x.shape
+        E, _, ff = down.shape
+        y = torch.empty((n, ff), dtype=self.dtype, device=self.device)
+        z = torch.empty((E, n, width), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_experts_dense(_p(x), _p(tokens), _p(table), E, _p(gate_up), gate_up.shape[1] * width, _p(down),
+                                               width * ff, _p(y), _p(z), _p(h), n, width, ff, table.shape[1], act, float(weight),
+                                               self._stream()), 2 * E + 1)
 
     def experts_combine(self, z, place, h, weight: float) -> None:
         """``h[t] += weight * sum_k z[place[t, k]]`` in ascending k (``place`` < 0: nothing)."""

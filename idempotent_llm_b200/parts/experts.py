@@ -7,7 +7,9 @@ grouping wherever it holds the step's token ids.  Steps of many tokens use that:
 their experts, every expert with rows runs the gated feed-forward's two matrix products on its slice, and the
 outputs are added back in the order of a token's choices.  Steps of few tokens (and steps whose tokens exist on the
 device only: captured single-token steps) look the experts up on the device, and every (token, choice) streams its
-expert's matrices.  Both add into the 32-bit stream; they differ in the order of their sums, not in what is summed.
+expert's matrices; from a few pairs per expert on, such a step instead runs every expert over all its tokens with the
+library's matrix products and lets each token pick its own experts' outputs.  All add into the 32-bit stream; they
+differ in the order of their sums, not in what is summed.
 """
 
 from __future__ import annotations
@@ -21,6 +23,9 @@ from .mlp import ACTIVATIONS
 
 # steps with at least this many (token, choice) pairs group their rows by expert (where the host has the tokens)
 GROUP_FROM = 256
+# steps that cannot group (their token ids are on the device only) with at least this many (token, choice) pairs per
+# expert run every expert over all tokens with the library's matrix products
+DENSE_FROM = 4
 
 
 @FEED_FORWARDS.register("table_experts")
@@ -76,6 +81,8 @@ class TableExperts(FeedForward):
             if ids is None:
                 ids = ctx.memo["host_token_array"] = np.concatenate([np.asarray(t, dtype=np.int64) for t in toks])
             self._grouped(x, ids, h)
+        elif self.fused and n * s.top >= DENSE_FROM * s.n_experts:
+            K.experts_dense(x, ctx.tokens, self.table, self.gate_up, self.down, h, self.act, 1.0 / s.top)
         else:
             K.experts_few(x, ctx.tokens, self.table, self.gate_up, self.row_stride, self.up_off, self.down, h, self.act, 1.0 / s.top)
         return None if residual is not None else h.unsqueeze(0)

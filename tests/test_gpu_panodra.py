@@ -203,8 +203,9 @@ def test_dense_feed_forward_with_the_square_of_relu(dtype):
 @pytest.mark.parametrize("hidden,inter,experts,top,n", [(64, 48, 5, 3, 7), (64, 48, 5, 3, 300), (20, 12, 3, 2, 40), (32, 16, 1, 1, 200),
                                                         (128, 96, 9, 2, 1000)])
 def test_table_experts_few_tokens_and_grouped_by_expert(dtype, hidden, inter, experts, top, n):
-    """Steps of few tokens look the experts up on the device; steps of many tokens whose ids the host holds run grouped
-    by expert; both against the plain sum.  An expert no token of the step uses has no rows."""
+    """Steps of few tokens look the experts up on the device (token by token, expert by expert, or every expert over
+    all tokens, by the step's size); steps of many tokens whose ids the host holds run grouped by expert; all against
+    the plain sum.  An expert no token of the step uses has no rows."""
     rt = _rt(dtype)
     V = 23
     spec = TableExpertsSpec(hidden=hidden, intermediate=inter, n_experts=experts, top=top, vocab_size=V)
