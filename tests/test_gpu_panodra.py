@@ -112,6 +112,8 @@ LATENT_SHAPES = {
                                         position=RotarySpec(5e5, 6, 1 << 20, variant="interleaved")),
     "more heads than a block has warps": _latent_spec(hidden=48, n_heads=11, plain_dim=8, rot_dim=4, value_dim=8, kv_rank=16,
                                                       position=RotarySpec(1e4, 4, 1 << 20, variant="interleaved")),
+    "twenty heads on fragments": _latent_spec(hidden=64, n_heads=20, plain_dim=16, rot_dim=16, value_dim=24, kv_rank=32,
+                                              position=RotarySpec(1e4, 16, 1 << 20, variant="interleaved"), softmax_scale=0.2),
     "tensor-core head 64": _latent_spec(hidden=64, n_heads=4, plain_dim=32, rot_dim=32, value_dim=48, kv_rank=64,
                                         position=RotarySpec(1e4, 32, 1 << 20, variant="interleaved"), softmax_scale=0.12),
     "tensor-core head 128, wide latent": _latent_spec(hidden=64, n_heads=2, plain_dim=64, rot_dim=16, value_dim=128, kv_rank=288,
