@@ -539,7 +539,10 @@ class Kernels:
         gp = self.lib.idm_attention_tc_heads_per_tile(n_q, n_kv)
         tok = 128 // gp
         R = self.attention_run_blocks
-        tiles = ctx.memo.get(("attention_tc_tiles", gp))
+        # (the spread of shared tiles over the pool depends on the number of head groups: layers with other head counts
+        # have plans of their own)
+        memo_key = ("attention_tc_tiles", gp, n_q // gp)
+        tiles = ctx.memo.get(memo_key)
         if tiles is None and ctx.single_token:
             # one tile per sequence: the same list for every step of that many sequences (kept, so that a
             # step being captured into a graph copies nothing from the host)
@@ -576,7 +579,7 @@ class Kernels:
             host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items], pool], dtype=torch.int32)
             dev = host.to(self.device)
             plan = (dev[2].data_ptr(), max_parts, per, slots_used) if slots_used else (None, 0, 0, 0)
-            tiles = ctx.memo[("attention_tc_tiles", gp)] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), rows_cap, plan)
+            tiles = ctx.memo[memo_key] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), rows_cap, plan)
         _, tile_seq, tile_start, n_tiles, rows_cap = tiles[:5]
         tile_pool, max_parts, per, pool_slots = tiles[5] if len(tiles) > 5 else (None, 0, 0, 0)
         # an upper bound of the key blocks any tile has (a captured step is replayed at growing lengths)

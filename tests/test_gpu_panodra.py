@@ -352,6 +352,32 @@ def test_unequal_batch_against_each_alone_with_slots_and_pages_used_again(panodr
     assert lm.engine.cache.pages_held() == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_through_layers_of_growing_head_counts(tmp_path, dtype):
+    """1 200 tokens (the tensor-core kernel shares a long tile's runs among several blocks and spreads them over a pool
+    by head group) through a layer of 2 heads followed by layers of 8 and 5: what one layer's plan holds must not
+    serve another's head count.  Then 20 single tokens beside a second, shorter sequence."""
+    cfg = helpers.panodra_config([
+        helpers.panodra_layer(heads=2, dim=32, rot_dim=32, vdim=48, kv_rank=64, scale=0.12, ff=96),
+        helpers.panodra_layer(sink=True, heads=8, dim=16, rot_dim=16, vdim=16, kv_rank=32, scale=0.18, mlp="moe", ff=32, experts=3, top=2),
+        helpers.panodra_layer(heads=5, dim=48, rot_dim=16, vdim=72, kv_rank=96, scale=0.12, mlp=None)],
+        vocab=300, width=128, loop=(0, 2, 2), logit_scale=1.0, softcap=20.0)
+    d = helpers.make_panodra_dir(cfg, str(tmp_path), seed=7, dtype=DT[dtype], std=0.08)
+    T, V = 1220, 300
+    a, b = helpers.rand_ids(T, V, 3), helpers.rand_ids(150, V, 4)
+    want_a, want_b = _plain_logits(d, a), _plain_logits(d, b)
+    lm = api.load(d, dtype=dtype, max_tokens=2048)
+    sa, sb = lm.engine.open(), lm.engine.open()
+    places = list(range(0, T - 20, 13))
+    g = lm.engine.step([(sa, a[:T - 20]), (sb, b[:130])], [places, [129]])
+    assert _close(g[:len(places)], want_a[places], dtype) and _close(g[len(places):], want_b[129:130], dtype)
+    rows_a, rows_b = [], []
+    for k in range(20):
+        g = lm.engine.step([(sa, [a[T - 20 + k]]), (sb, [b[130 + k]])])
+        rows_a.append(g[0:1]); rows_b.append(g[1:2])
+    assert _close(torch.cat(rows_a), want_a[T - 20:], dtype) and _close(torch.cat(rows_b), want_b[130:], dtype)
+
+
 def _far_key_model(tmp, dtype, sink):
     """A one-layer model whose first head looks for ONE key.  The embedding's first coordinate is -1 for every token but
     token 1 (+1); the latent's first number reads it (the other rows of the down projection are zero, so the normed
