@@ -134,6 +134,9 @@ def cmd_demo(args) -> int:
             print(f"  @{k:<4} tokens {t_at[k]}   logits {l_at[k]}")
     ok = True
     base = names[0]
+    # An architecture whose steps of different shapes take different kernels (a part says so: `same_bits_across_steps
+    # = False`) promises the same sums in another order: there the cuts are compared up to rounding
+    exact = bool(getattr(lm.model, "same_bits_across_steps", True))
     for n in names[1:]:
         ta, la, ra = results[base]
         tb, lb, rb = results[n]
@@ -142,8 +145,15 @@ def cmd_demo(args) -> int:
         worst = max(float((a[1] - b[1]).abs().max()) for a, b in zip(ra, rb))
         print(f"{n} vs {base}: tokens {'identical' if tdiv is None else f'diverge @ {tdiv}'}; logits "
               f"{'bit-identical' if ldiv is None else f'differ from step {ldiv}'} (max |diff| {worst:.3g})")
-        if ldiv is not None or tdiv is not None:
-            ok = False                      # both precisions promise identical bits across these cuts
+        if exact:
+            if ldiv is not None or tdiv is not None:
+                ok = False                  # both precisions promise identical bits across these cuts
+        else:
+            largest = max(float(a[1].abs().max()) for a in ra)
+            bound = (1e-4 if args.dtype == "float32" else 5e-2) * max(largest, 1e-30)
+            print(f"  (this architecture: equal up to rounding; bound {bound:.3g})")
+            if worst > bound:
+                ok = False
     record = {"artifact_sha256": sha, "dtype": args.dtype, "steps": args.steps,
               "chains": {n: {"tokens": results[n][0].prefixes, "logits": results[n][1].prefixes} for n in names}}
     if args.against:

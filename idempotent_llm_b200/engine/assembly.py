@@ -66,6 +66,9 @@ class CausalLM:
         self._programs = {}
         self.graph_safe = all(getattr(part, "graph_safe", True) for b in self.blocks
                               for part in vars(b).values())
+        # False if a part runs steps of different shapes on different kernels (the same sums in another order)
+        self.same_bits_across_steps = all(getattr(part, "same_bits_across_steps", True) for b in self.blocks
+                                          for part in vars(b).values())
 
     def program(self, cache):
         """The model's kernel calls over ``cache`` as a step program (``kernels/program.py``), made once; None

@@ -84,6 +84,9 @@ class Part:
     # False for a part that synchronises with the host inside ``forward`` (reads device values):
     # a model with such a part runs its single-token steps without CUDA graphs.
     graph_safe = True
+    # False for a part whose result for a token depends, in its last bits, on the step's shape (it runs prompts and
+    # single tokens on different kernels): tools that compare runs bit for bit then compare up to rounding.
+    same_bits_across_steps = True
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:

@@ -31,6 +31,7 @@ DENSE_FROM = 4
 @FEED_FORWARDS.register("table_experts")
 class TableExperts(FeedForward):
     accepts_residual = True
+    same_bits_across_steps = False      # whole prompts, portions and single tokens take different kernels
 
     @classmethod
     def declare(cls, spec, prefix):

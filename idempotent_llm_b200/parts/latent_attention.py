@@ -34,6 +34,7 @@ from .base import MIXERS, POSITIONS, Mixer
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     accepts_residual = True
+    same_bits_across_steps = False      # whole prompts, portions and single tokens take different kernels
 
     @classmethod
     def declare(cls, spec, prefix):

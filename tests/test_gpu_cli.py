@@ -53,3 +53,27 @@ def test_random_generate_and_demo(tmp_path):
     with open(chains + "float32") as f:
         rec = json.load(f)
     assert set(rec["chains"]) == {"b1", "b8", "split"} and len(rec["chains"]["b1"]["logits"]) == 16
+
+
+def test_the_same_commands_on_a_panodra_folder(tmp_path):
+    """``random`` from the preset, ``generate`` against the plain implementation's greedy tokens, and ``demo``, which
+    compares this architecture's three ways of running a prompt up to rounding (its steps of different shapes take
+    different kernels) and still demands the same tokens."""
+    import torch
+    import plain_panodra
+    d = str(tmp_path / "panodra-tiny")
+    _cli("random", "--size", "panodra-tiny", "--out", d, "--seed", "5")
+    cfg, w = helpers.read_model_dir(d)
+    ids = helpers.rand_ids(7, cfg["vocab"], 702)
+    p = _cli("generate", "--artifact", d, "--dtype", "float32", "--max-new", "5", "--prompt-ids", " ".join(map(str, ids)))
+    got = [int(t) for t in [l for l in p.stdout.splitlines() if l.startswith("request ")][0].split(":")[1].split()]
+    seq = list(ids)
+    for t in got:
+        lg = plain_panodra.forward(cfg, w, seq)[-1]
+        top2 = torch.topk(lg, 2).values
+        if float(top2[0] - top2[1]) > 1e-4:
+            assert t == int(lg.argmax())
+        seq.append(t)
+    for dtype in ("float32", "bfloat16"):
+        p = _cli("demo", "--artifact", d, "--steps", "12", "--dtype", dtype)
+        assert "equal up to rounding" in p.stdout and "VERDICT: consistent" in p.stdout, p.stdout
