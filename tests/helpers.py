@@ -245,7 +245,7 @@ PANODRA = {
     # run grouped by expert from 128 tokens on
     "T": lambda: panodra_config([
         panodra_layer(heads=4, dim=32, rot_dim=32, vdim=64, kv_rank=64, scale=0.12, ff=160),
-        panodra_layer(sink=True, heads=3, dim=64, rot_dim=32, vdim=80, kv_rank=96, scale=0.1, scaling=(4.0, 128, 16.0, 1.0),
+        panodra_layer(sink=True, heads=3, dim=72, rot_dim=24, vdim=88, kv_rank=96, scale=0.1, scaling=(6.0, 128, 16.0, 1.0),
                       mlp="moe", ff=64, experts=4, top=2)], vocab=211, width=128, loop=(0, 2, 2)),
 }
 
@@ -258,16 +258,16 @@ def panodra_random_config(seed: int) -> dict:
     def layer():
         rot_dim = r.choice([8, 16, 32, 64]); dim = r.choice([16, 32, 64, 96, 128])
         return panodra_layer(sink=r.random() < 0.5, heads=r.choice([1, 2, 4, 6, 8]), dim=dim, rot_dim=rot_dim,
-                             vdim=r.choice([16, 32, 64, 80, 128]), kv_rank=r.choice([32, 64, 96, 128, 256]),
-                             scale=r.choice([(dim + rot_dim) ** -0.5, 0.1, 0.05]), rot_base=r.choice([1e4, 2.5e5, 1e6]),
-                             scaling=r.choice([None, (4.0, 1024, 32.0, 1.0), (16.0, 64, 4.0, 0.5), (2.0, 256, 8.0, 2.0)]),
+                             vdim=r.choice([16, 32, 64, 72, 128]), kv_rank=r.choice([32, 64, 96, 160, 256]),
+                             scale=r.choice([(dim + rot_dim) ** -0.5, 0.1, 0.05]), rot_base=r.choice([1e4, 3e5, 1e6]),
+                             scaling=r.choice([None, (6.0, 2048, 16.0, 1.0), (16.0, 64, 4.0, 0.5), (2.0, 256, 8.0, 2.0)]),
                              mlp=r.choice(["dense", "moe", "moe", None]), ff=r.choice([64, 96, 160]),
                              experts=r.choice([2, 4, 9]), top=r.choice([1, 2]))
     n = r.choice([1, 2, 3, 4])
     a = r.randrange(n); b = r.randrange(a + 1, n + 1)
     return panodra_config([layer() for _ in range(n)], vocab=r.choice([128, 500, 1000]), width=r.choice([64, 96, 128, 256]),
                           eps=r.choice([1e-5, 1e-6]), loop=r.choice([None, (a, b, r.choice([1, 2, 3]))]),
-                          logit_scale=r.choice([None, 0.5, 2.0]), softcap=r.choice([None, 30.0, 8.0]))
+                          logit_scale=r.choice([None, 0.4, 2.0]), softcap=r.choice([None, 25.0, 8.0]))
 
 
 def make_panodra_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.2, edit=None) -> str:
