@@ -21,13 +21,26 @@ __device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* _
     return warp_sum(s);
 }
 
-// two rows against two vectors at once: four 16-byte loads of a lane are in flight before the first is used
+// two rows against two vectors at once: eight (long rows) or four 16-byte loads of a lane are in flight before the
+// first is used; a sum's order depends on the row's length alone
 __device__ __forceinline__ void row_dot2(const T* __restrict__ w0, const T* __restrict__ w1, const float* __restrict__ x0,
                                          const float* __restrict__ x1, int K, int lane, bool vec, float& r0, float& r1) {
     float s0 = 0.f, s1 = 0.f;
     if (vec) {
         constexpr int VN = Vec16<T>::N;
         int d = lane * VN;
+        for (; d + 96 * VN < K; d += 128 * VN) {             // four pieces of each row: eight loads before the first use
+            Vec16<T> a[4], b[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { a[c].load(w0 + d + c * 32 * VN); b[c].load(w1 + d + c * 32 * VN); }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int e = 0; e < VN; ++e) {
+                    s0 = fmaf(x0[d + c * 32 * VN + e], a[c].get(e), s0);
+                    s1 = fmaf(x1[d + c * 32 * VN + e], b[c].get(e), s1);
+                }
+        }
         for (; d + 32 * VN < K; d += 64 * VN) {
             Vec16<T> a0, a1, b0, b1;
             a0.load(w0 + d); b0.load(w1 + d); a1.load(w0 + d + 32 * VN); b1.load(w1 + d + 32 * VN);
