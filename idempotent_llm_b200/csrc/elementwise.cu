@@ -689,3 +689,18 @@ extern "C" int idm_logit_cap(float* logits, long long n, float scale, float cap,
     IDM_LAUNCH_CHECK("logit_cap");
     return 0;
 }
+
+#if defined(IDM_BF16)
+// h += down . act(up . x) from one call: the up product (32-bit z), the activation (y, storage type), the down
+// product added into the stream: the calls a dense feed-forward makes, with the same arguments
+extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, int N, int K, cudaStream_t stream);
+extern "C" int idm_gemm_bf16_residual(const void* x, const void* w, float* h, int M, int N, int K, cudaStream_t stream);
+
+extern "C" int idm_dense_ff(const void* x, const void* w_up, const void* w_down, float* z, void* y, float* h, int n_tokens,
+                            int width, int ff, int act, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    if (idm_gemm_bf16(x, w_up, z, n_tokens, ff, width, stream)) return 1;
+    if (idm_act_cast(z, y, (long long)n_tokens * ff, act, stream)) return 1;
+    return idm_gemm_bf16_residual(y, w_down, h, n_tokens, width, ff, stream);
+}
+#endif

@@ -351,6 +351,19 @@ extern "C" int idm_experts_grouped(const void* xg, const int* counts, int n_expe
     return 0;
 }
 
+// The grouped feed-forward of a step from one call: rows gathered in the order of their experts (src: grouped row ->
+// token), every expert's two products, outputs added into the stream in the order of a token's choices (place:
+// (token, choice) -> grouped row).  xg, y, z: scratch [n_tokens * top, width | ff | width].
+extern "C" int idm_experts_grouped_step(const void* x, const int* src, const int* place, const int* counts, int n_experts,
+                                        const void* gate_up, long long gate_up_stride, const void* down, long long down_stride,
+                                        void* xg, void* y, float* z, float* h, int n_tokens, int top, int width, int ff, int act,
+                                        float weight, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    if (idm_rows_gather(x, src, xg, n_tokens * top, width, stream)) return 1;
+    if (idm_experts_grouped(xg, counts, n_experts, gate_up, gate_up_stride, down, down_stride, y, z, width, ff, act, stream)) return 1;
+    return idm_experts_combine(z, place, h, n_tokens, width, top, weight, stream);
+}
+
 // Single-token steps of many sequences, whose ids exist on the device only and whose shapes must not change from
 // step to step: EVERY expert's feed-forward over ALL the step's tokens with the library's matrix products (what such a
 // step has to do anyway is to stream every expert's matrices once: the products it does not need ride along), then

@@ -103,6 +103,8 @@ SIGNATURES = {
     "idm_rows_gather": (c_int, "pppiip"),
     "idm_experts_grouped": (c_int, "ppipqpqppiiip"),
     "idm_experts_dense": (c_int, "pppipqpqpppiiiiifp"),
+    "idm_experts_grouped_step": (c_int, "ppppipqpqppppiiiiifp"),
+    "idm_dense_ff": (c_int, "ppppppiiiip"),
     "idm_experts_combine": (c_int, "pppiiifp"),
     "idm_add_dyt": (c_int, "ppiqppfppiip"),
     "idm_act_cast": (c_int, "ppqip"),
@@ -1003,6 +1005,34 @@ class Kernels:
         self._check(self.lib.idm_experts_dense(_p(x), _p(tokens), _p(table), E, _p(gate_up), gate_up.shape[1] * width, _p(down),
                                                width * ff, _p(y), _p(z), _p(h), n, width, ff, table.shape[1], act, float(weight),
                                                self._stream()), 2 * E + 1)
+
+    def experts_grouped_step(self, x, src, place, counts, gate_up, down, h, act: int, weight: float) -> None:
+        """Gather, every expert's two products, and the sum back into ``h``, from one call (see ``experts_grouped``;
+        ``src [rows]``: grouped row -> token; ``place [tokens, top]``: (token, choice) -> grouped row)."""
+        self._need(x, self.dtype, "experts input")
+        self._need(h, torch.float32, "residual stream")
+        n, width = x.shape
+        E, _, ff = down.shape
+        top = place.shape[1]
+        xg = torch.empty((n * top, width), dtype=self.dtype, device=self.device)
+        y = torch.empty((n * top, ff), dtype=self.dtype, device=self.device)
+        z = torch.empty((n * top, width), dtype=torch.float32, device=self.device)
+        with_rows = int((counts > 0).sum())
+        self._check(self.lib.idm_experts_grouped_step(_p(x), _p(src), _p(place), counts.ctypes.data, E, _p(gate_up),
+                                                      gate_up.shape[1] * width, _p(down), width * ff, _p(xg), _p(y), _p(z), _p(h),
+                                                      n, top, width, ff, act, float(weight), self._stream()), 2 * with_rows + 2)
+
+    def dense_ff(self, x, w_up, w_down, h, act: int) -> None:
+        """``h += w_down . act(w_up . x)`` from one call: the up product, the activation, the down product with the sum
+        into the stream as its epilogue (bfloat16)."""
+        M, ff, Kd = self._gemm_shape(x, w_up)
+        self._need(w_down, self.dtype, "down weight")
+        self._need(h, torch.float32, "residual stream")
+        if tuple(w_down.shape) != (Kd, ff) or tuple(h.shape) != (M, Kd) or ff % 8:
+            raise KernelError(f"dense_ff: up {tuple(w_up.shape)}, down {tuple(w_down.shape)}, stream {tuple(h.shape)}")
+        z = torch.empty((M, ff), dtype=torch.float32, device=self.device)
+        y = torch.empty((M, ff), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_dense_ff(_p(x), _p(w_up), _p(w_down), _p(z), _p(y), _p(h), M, Kd, ff, act, self._stream()), 3)
 
     def experts_combine(self, z, place, h, weight: float) -> None:
         """``h[t] += weight * sum_k z[place[t, k]]`` in ascending k (``place`` < 0: nothing)."""

@@ -91,7 +91,8 @@ class TableExperts(FeedForward):
     def _grouped(self, x, tokens, h):
         s, K = self.spec, self.rt.kernels
         n, top = tokens.shape[0], s.top
-        choice = self.table_host[tokens].reshape(-1)                       # [n * top]: expert of (token, k)
+        # [n * top]: expert of (token, k); as 16-bit keys where they fit (a stable sort of those is a radix sort)
+        choice = self.table_host[tokens].reshape(-1).astype(np.int16 if s.n_experts < 32768 else np.int32)
         order = np.argsort(choice, kind="stable")                          # grouped rows -> (token, k)
         counts = np.bincount(choice, minlength=s.n_experts)
         place = np.empty(n * top, dtype=np.int32)

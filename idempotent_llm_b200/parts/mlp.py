@@ -100,8 +100,8 @@ class DenseMLP(FeedForward):
 
     def forward(self, x, ctx, residual=None):
         K = self.rt.kernels
-        y = K.act_cast(K.gemm_store(x, self.w_up, **self.pad), self.act)
         if residual is not None and getattr(K, "fused", False) and not self.pad:
-            K.gemm_residual(y, self.w_down, residual)
+            K.dense_ff(x, self.w_up, self.w_down, residual, self.act)       # the three calls below from one
             return None
+        y = K.act_cast(K.gemm_store(x, self.w_up, **self.pad), self.act)
         return K.gemm(y, self.w_down, **self.pad)
