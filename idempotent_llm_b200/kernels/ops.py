@@ -977,21 +977,6 @@ class Kernels:
         self._check(self.lib.idm_rows_gather(_p(x), _p(src), _p(out), src.numel(), x.shape[1], self._stream()))
         return out
 
-    def experts_grouped(self, xg, counts, gate_up, down, act: int) -> torch.Tensor:
-        """Rows grouped by expert (``counts[e]`` rows of expert e, one group after another) through every expert's gated
-        feed-forward: ``z[rows of e] = down[e] (act(gate[e] x) * up[e] x)``, 32-bit ``[rows, width]``.  One call: the
-        library runs the two matrix products of every expert that has rows (``gate_up`` in the layout of
-        ``tile_gate_up``).  ``counts``: a contiguous int32 numpy array on the host."""
-        self._need(xg, self.dtype, "grouped rows")
-        rows, width = xg.shape
-        E, _, ff = down.shape
-        y = torch.empty((rows, ff), dtype=self.dtype, device=self.device)
-        z = torch.empty((rows, width), dtype=torch.float32, device=self.device)
-        with_rows = int((counts > 0).sum())
-        self._check(self.lib.idm_experts_grouped(_p(xg), counts.ctypes.data, E, _p(gate_up), gate_up.shape[1] * width, _p(down),
-                                                 width * ff, _p(y), _p(z), width, ff, act, self._stream()), 2 * with_rows)
-        return z
-
     def experts_dense(self, x, tokens, table, gate_up, down, h, act: int, weight: float) -> None:
         """``h[t] += weight * sum_k ff_e(x_t)``, ``e = table[tokens[t], k]``, by running EVERY expert over all the step's
         tokens with the library's matrix products and letting each token pick its own (single-token steps of many
@@ -1007,8 +992,11 @@ class Kernels:
                                                self._stream()), 2 * E + 1)
 
     def experts_grouped_step(self, x, src, place, counts, gate_up, down, h, act: int, weight: float) -> None:
-        """Gather, every expert's two products, and the sum back into ``h``, from one call (see ``experts_grouped``;
-        ``src [rows]``: grouped row -> token; ``place [tokens, top]``: (token, choice) -> grouped row)."""
+        """A step's rows grouped by expert through every expert's gated feed-forward, from one call into the library:
+        rows gathered in the order of their experts (``src [rows]``: grouped row -> token), the gated product (activation
+        in its epilogue, ``gate_up`` in the layout of ``tile_gate_up``) and the down product of every expert that has
+        rows (``counts``: rows per expert, a contiguous int32 numpy array on the host), and the outputs added into ``h``
+        in the order of a token's choices (``place [tokens, top]``: (token, choice) -> grouped row)."""
         self._need(x, self.dtype, "experts input")
         self._need(h, torch.float32, "residual stream")
         n, width = x.shape

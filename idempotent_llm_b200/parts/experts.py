@@ -98,22 +98,18 @@ class TableExperts(FeedForward):
         place = np.empty(n * top, dtype=np.int32)
         place[order] = np.arange(n * top, dtype=np.int32)                  # (token, k) -> grouped row
         both = torch.from_numpy(np.concatenate([(order // top).astype(np.int32), place])).to(x.device, non_blocking=True)
-        xg = K.rows_gather(x, both[:n * top])
-        if self.fused:                      # every expert's two products from one call into the library
-            z = K.experts_grouped(xg, np.ascontiguousarray(counts, dtype=np.int32), self.gate_up, self.down, self.act)
-            K.experts_combine(z, both[n * top:].view(n, top), h, 1.0 / top)
+        if self.fused:                      # gather, every expert's two products and the sum back: one call into the library
+            K.experts_grouped_step(x, both[:n * top], both[n * top:].view(n, top), np.ascontiguousarray(counts, dtype=np.int32),
+                                   self.gate_up, self.down, h, self.act, 1.0 / top)
             return
+        xg = K.rows_gather(x, both[:n * top])
         z = torch.empty((n * top, s.hidden), dtype=torch.float32, device=x.device)
         at = 0
         for e in range(s.n_experts):
             c = int(counts[e])
             if not c:
                 continue
-            xe = xg[at:at + c]
-            if self.fused:
-                y = K.gemm_gated(xe, self.gate_up[e], s.intermediate, self.act)
-            else:
-                y = K.gated_act(K.gemm_store(xe, self.gate_up[e]), self.act)
+            y = K.gated_act(K.gemm_store(xg[at:at + c], self.gate_up[e]), self.act)      # (no fused epilogue here: 32-bit)
             K.gemm_store(y, self.down[e], out=z[at:at + c])
             at += c
         K.experts_combine(z, both[n * top:].view(n, top), h, 1.0 / top)
